@@ -1,0 +1,67 @@
+// Shared host-side plumbing of the library: status codes, the thread-local error message,
+// per-device state (properties, the scratch arena, the device status word).
+//
+// Error model of the C-ABI: every entry point returns an int status and leaves a message
+// readable through spk_last_error(). The C++ namespace-spark shim turns SPK_INVALID into
+// std::invalid_argument and the others into std::runtime_error, which is the error behaviour
+// of the reference's host API (reference include/spark/common.cuh:22-37).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/spk.h"
+
+namespace spk {
+
+// printf-style; stores the message for spk_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+#define SPK_REQUIRE(cond, ...)                                   \
+    do {                                                         \
+        if (!(cond)) return ::spk::fail(SPK_INVALID, __VA_ARGS__); \
+    } while (0)
+
+#define SPK_CUDA(call)                                                                        \
+    do {                                                                                      \
+        cudaError_t e__ = (call);                                                             \
+        if (e__ != cudaSuccess)                                                               \
+            return ::spk::fail(SPK_CUDA_ERROR, "%s failed: %s (%s:%d)", #call,                \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);                  \
+    } while (0)
+
+#define SPK_CHECK_LAUNCH() SPK_CUDA(cudaGetLastError())
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Scratch every split-K kernel shares on one device. Allocated once per device on first use
+// (or by spk_init), never moved or freed, so pointers baked into captured CUDA graphs stay
+// valid. The kernels leave partials and counters zeroed when they finish.
+struct DeviceState {
+    int device = -1;
+    int sm_count = 0;
+    int64_t l2_bytes = 0;
+    int mem_clock_khz = 0;
+    int bus_width_bits = 0;
+    int max_smem_optin = 0;
+    float* partials = nullptr;      // kPartialFloats fp32, zero between launches
+    unsigned* counters = nullptr;   // kCounters, zero between launches
+    int* status = nullptr;          // kStatusWords device ints: [0] first error code of a kernel
+    bool ready = false;
+};
+
+constexpr int64_t kPartialFloats = int64_t{64} * 65536;  // 64 tokens x 65536 columns, 16 MiB
+constexpr int kCounters = 1 << 16;
+constexpr int kStatusWords = 8;
+
+// State of the current device; *out stays valid for the life of the process.
+int device_state(DeviceState** out);
+
+}  // namespace spk

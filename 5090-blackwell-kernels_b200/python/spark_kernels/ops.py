@@ -1,0 +1,70 @@
+"""Python-level wrappers of the quantized-GEMM ops: the surface of the reference's
+python/spark_kernels/ops.py:196-353 for this path (same names, arguments and defaults)."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _C
+
+W4_GROUP = 128  # k per scale (and zero point) of the int4 weights
+
+
+def w4_quantize(w: torch.Tensor, asym: bool = False):
+    """Round-to-nearest int4 quantization of a [K, N] bfloat16 weight (the x @ w layout), one
+    scale per 128 consecutive k of a column, computed in fp32.
+
+    Symmetric: s = bf16(max|w| / 7), q = clamp(rint(w / s), -8, 7) + 8, so w ~ (q - 8) s.
+    asym=True: lo = min(min w, 0), hi = max(max w, 0), s = bf16((hi - lo) / 15),
+    z = clamp(rint(-lo / s), 0, 15), q = clamp(rint(w / s) + z, 0, 15), so w ~ (q - z) s.
+    Returns (qweight [K/8, N] int32 in GPTQ's packing, scales [K/128, N] bf16, zeros uint8 or
+    None). K must be a multiple of 128 and N of 16."""
+    return _C.w4_quantize(w, asym)
+
+
+def w4_repack(qweight: torch.Tensor) -> torch.Tensor:
+    """qweight [K/8, N] int32 -> the layout `w4gemm` streams, int32 [N/16, 2K]. Once per weight."""
+    return _C.w4_repack(qweight)
+
+
+class W4Weight:
+    """An int4 weight ready for `w4gemm`: repacked codes, scales and optional zero points of a
+    [K, N] (in_features x out_features) matrix."""
+
+    def __init__(self, packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor | None = None):
+        self.packed = packed
+        self.scales = scales
+        self.zeros = zeros
+
+    @staticmethod
+    def quantize(w: torch.Tensor, asym: bool = False) -> "W4Weight":
+        qweight, scales, zeros = w4_quantize(w, asym)
+        return W4Weight(w4_repack(qweight), scales, zeros)
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        """(K, N) of the weight it stands for."""
+        return self.packed.shape[1] // 2, self.packed.shape[0] * 16
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.packed, self.scales, self.zeros) if t is not None)
+
+
+def w4gemm(a: torch.Tensor, w, scales: torch.Tensor | None = None, zeros: torch.Tensor | None = None,
+           variant: int = -1, out: torch.Tensor | None = None) -> torch.Tensor:
+    """W4A16 GEMM: a [M, K] bf16 @ int4 weight [K, N] -> [M, N] bf16, fp32 accumulate. `w` is a
+    `W4Weight`, or the packed codes with `scales` (and `zeros`) given separately. Every product
+    uses the weight bf16((q - z) s), rounded once. K % 128 == 0, N % 16 == 0, any M >= 1.
+    Variant 2 (default) is the bulk-copy weight stream, 3 its batch-invariant form, 0 and 1
+    the simple rungs below."""
+    if isinstance(w, W4Weight):
+        if scales is not None or zeros is not None:
+            raise ValueError("pass scales and zeros inside the W4Weight, not separately")
+        w, scales, zeros = w.packed, w.scales, w.zeros
+    if scales is None:
+        raise ValueError("w4gemm needs the scales of the packed weight")
+    return _C.w4gemm(a, w, scales, zeros, variant, out)
+
+
+def num_variants(name: str) -> int:
+    return _C.num_variants(name)

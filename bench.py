@@ -1,0 +1,325 @@
+"""Benchmark of the int4 W4A16 decode GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE config 1, "llama3_8b_mlp_int4_decode"): the Llama-3-8B MLP projections with
+int4 group-128 weights, gate|up fused (N = 28672, K = 4096) and down (N = 4096, K = 14336), at
+M = 1, 16 and 64 tokens. One step runs both GEMMs of LAYERS distinct layers at each M, so the
+weights streamed between two uses of the same layer (1.4 GB) far exceed the 126 MB L2: the
+inputs are larger than L2, no flush is needed. The step is captured once in a CUDA graph and
+replayed; timing is CUDA events around the K replays, max over ranks.
+
+metric/value: algorithmic bytes moved per second (the reference's own traffic model:
+2MK + KN/2 + 2(K/128)N + 2MN per GEMM), whole job. roofline: the same figure per launch of the
+stream kernel against the measured HBM copy bandwidth. e2e: the same metric with, every step,
+the activations copied from pinned host memory and the last layer's outputs read back.
+cpu_baseline / --impl reference: the CPU restatement of the reference's arithmetic (the
+reference has no CPU int4 GEMM of its own) timed on the host cores on a bounded sample.
+
+With N > 1 the projections run tensor parallel as the north star asks: gate|up column-split
+(no communication), down row-split followed by one NCCL all-reduce of the [M, 4096] output;
+total work is fixed, so scaling is "strong".
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "5090-blackwell-kernels_b200", "python")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+HIDDEN, INTER = 4096, 14336
+MS = (1, 16, 64)
+LAYERS = 16
+WORKLOAD = "llama3_8b_mlp_int4_decode"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def alg_bytes(M: int, N: int, K: int) -> int:
+    """Traffic floor of one symmetric W4A16 GEMM (reference scripts/shape_utils.py:310-321)."""
+    return 2 * M * K + K * N // 2 + 2 * (K // 128) * N + 2 * M * N
+
+
+def step_bytes(layers: int) -> int:
+    return layers * sum(alg_bytes(m, 2 * INTER, HIDDEN) + alg_bytes(m, HIDDEN, INTER) for m in MS)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region: SM clock and throttle reasons."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU arm -------------------------------------------------------------------------------------
+
+def cpu_sample(threads: int = 0):
+    """One bounded sample of the workload on the host: one layer's gate|up and down at M = 1, 16
+    (the M = 64 pair alone is 11 G multiply-adds; it is left out to keep the sample near 10-20 s).
+    Returns (GB/s of algorithmic bytes, seconds, threads, description)."""
+    import numpy as np
+
+    from oracle import oracle as orc
+
+    orc.lib()
+    rng = np.random.default_rng(0)
+    ms = (1, 16)
+    total, secs = 0, 0.0
+    for (K, N) in ((HIDDEN, 2 * INTER), (INTER, HIDDEN)):
+        packed = rng.integers(-2 ** 31, 2 ** 31 - 1, size=(N // 16, 2 * K), dtype=np.int64).astype(np.int32)
+        scales = orc.bf16_bits(np.abs(rng.standard_normal((K // 128, N)).astype(np.float32)) * 0.02)
+        for M in ms:
+            a = orc.bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+            t0 = time.perf_counter()
+            orc.w4gemm(a, packed, scales, None, threads=threads)
+            secs += time.perf_counter() - t0
+            total += alg_bytes(M, N, K)
+    used = threads if threads > 0 else orc.max_threads()
+    return total / secs / 1e9, secs, used, "1 layer: gate|up 28672x4096 and down 4096x14336 at M=1,16"
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for i in range(args.warmup + args.steps):
+        gbs, secs, used, sample = cpu_sample(0)
+        if i >= args.warmup:
+            vals.append((gbs, secs))
+    value = sum(v for v, _ in vals) / len(vals)
+    ms = 1e3 * sum(s for _, s in vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "int4_decode_gemm_gbps", "value": round(value, 4), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint4->fp32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": used, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arm -------------------------------------------------------------------------------------
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import spark_kernels as sk
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tp = world
+    assert (2 * INTER) % (16 * tp) == 0 and INTER % (128 * tp) == 0
+    sk._C.init()
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def rand_weight(K, N):
+        packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 16, 2 * K), dtype=torch.int32, device=dev, generator=gen)
+        scales = (torch.randn(K // 128, N, device=dev, generator=gen).abs() * 0.02).to(torch.bfloat16)
+        return packed, scales
+
+    # column split of gate|up (N / tp columns), row split of down (K / tp rows)
+    gu = [rand_weight(HIDDEN, 2 * INTER // tp) for _ in range(LAYERS)]
+    dn = [rand_weight(INTER // tp, HIDDEN) for _ in range(LAYERS)]
+    x = {m: torch.randn(m, HIDDEN, device=dev, generator=gen).to(torch.bfloat16) for m in MS}
+    h = {m: torch.randn(m, INTER // tp, device=dev, generator=gen).to(torch.bfloat16) for m in MS}
+    y_gu = {m: torch.empty(m, 2 * INTER // tp, device=dev, dtype=torch.bfloat16) for m in MS}
+    y_dn = {m: torch.empty(m, HIDDEN, device=dev, dtype=torch.bfloat16) for m in MS}
+    launches_per_step = 0
+
+    def step():
+        n = 0
+        for m in MS:
+            for layer in range(LAYERS):
+                sk.w4gemm(x[m], gu[layer][0], gu[layer][1], None, -1, y_gu[m])
+                sk.w4gemm(h[m], dn[layer][0], dn[layer][1], None, -1, y_dn[m])
+                n += 2
+                if world > 1:
+                    dist.all_reduce(y_dn[m])
+        return n
+
+    # eager warm-up on a side stream, then capture one step
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launches_per_step = step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+
+    # end to end: activations from pinned host memory every step, outputs read back every step
+    pin_x = {m: torch.randn(m, HIDDEN).to(torch.bfloat16).pin_memory() for m in MS}
+    pin_h = {m: torch.randn(m, INTER // tp).to(torch.bfloat16).pin_memory() for m in MS}
+    out_gu = {m: torch.empty(m, 2 * INTER // tp, dtype=torch.bfloat16).pin_memory() for m in MS}
+    out_dn = {m: torch.empty(m, HIDDEN, dtype=torch.bfloat16).pin_memory() for m in MS}
+    h2d = sum(t.numel() * 2 for t in list(pin_x.values()) + list(pin_h.values()))
+    d2h = sum(t.numel() * 2 for t in list(out_gu.values()) + list(out_dn.values()))
+
+    def e2e_step():
+        for m in MS:
+            x[m].copy_(pin_x[m], non_blocking=True)
+            h[m].copy_(pin_h[m], non_blocking=True)
+        graph.replay()
+        for m in MS:
+            out_gu[m].copy_(y_gu[m], non_blocking=True)
+            out_dn[m].copy_(y_dn[m], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    status = sk._C.device_status()
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e, float(status)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e, status = t[0].item(), t[1].item(), int(t[2].item())
+    assert status == 0, f"a kernel reported device status {status}"
+
+    if rank == 0:
+        total_bytes = step_bytes(LAYERS)  # whole job: the shards of all ranks add up to the full weights
+        value = total_bytes * args.steps / (ms_total * 1e-3) / 1e9
+        e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+        peak, which = measured_peak()
+        per_launch_bytes = total_bytes / tp / launches_per_step
+        per_launch_ms = ms_total / args.steps / launches_per_step
+        achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            gbs, secs, used, sample = cpu_sample(0)
+            cpu = {"value": round(gbs, 4), "unit": "GB/s", "cores": used, "kind": "port", "sample": sample,
+                   "seconds": round(secs, 2)}
+        line = {
+            "metric": "int4_decode_gemm_gbps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_total / args.steps, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint4->fp32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": LAYERS, "M": list(MS), "gate_up": [2 * INTER, HIDDEN],
+                       "down": [HIDDEN, INTER], "group": 128, "parallelism": f"tp{tp}",
+                       "l2": "inputs larger than L2 (1.4 GB of weights per step)", "launch": "cuda graph"},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_source": which, "traffic": None,
+                         "kernel": "w4_stream_kernel", "bytes_per_launch": int(per_launch_bytes)},
+            "cpu_baseline": cpu,
+            "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,71 @@
+/*
+ * spk.h -- C ABI of the B200 (sm_100a) quantized-GEMM library.
+ *
+ * This is the drop-in boundary: plain C, plain pointers and sizes, no C++ or torch types.
+ * Every function that launches work is asynchronous on `stream` (a cudaStream_t passed as
+ * void*; NULL is the legacy default stream), takes DEVICE pointers owned by the caller, and
+ * returns a status code; spk_last_error() gives the message of the calling thread's last
+ * failure. Matrices are row-major and contiguous.
+ *
+ * Each entry point replaces one function of the reference's host API
+ * (include/spark/kernels.h in the reference); the citation beside it names the declaration.
+ * The C++ header include/spark/kernels.h of this repository re-exports them under the
+ * reference's own names and signatures (namespace spark, exceptions instead of codes).
+ */
+#ifndef SPK_H_
+#define SPK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPK_API __attribute__((visibility("default")))
+
+enum {
+    SPK_OK = 0,
+    SPK_INVALID = 1,     /* host-side validation failed (reference: std::invalid_argument) */
+    SPK_CUDA_ERROR = 2,  /* a CUDA call failed (reference: std::runtime_error) */
+    SPK_TIMEOUT = 3,     /* a bounded device-side wait gave up (read by spk_device_status) */
+    SPK_UNSUPPORTED = 4  /* the device is not an sm_100 part */
+};
+
+/* Message of the last failure on the calling thread ("" if none). */
+SPK_API const char* spk_last_error(void);
+/* Library version string. */
+SPK_API const char* spk_version(void);
+/* Allocates the per-device scratch (16 MiB of fp32 partials, counters, a status word) for the
+ * current device. Every kernel that needs it calls this lazily; call it yourself before
+ * capturing a CUDA graph so that no allocation happens during capture. */
+SPK_API int spk_init(void);
+/* Synchronizes the stream and reads the device status word: *code is SPK_OK unless a kernel's
+ * bounded wait timed out (SPK_TIMEOUT); the word is cleared. */
+SPK_API int spk_device_status(void* stream, int* code);
+
+/* ---- int4 W4A16 ------------------------------------------------------------------------- */
+
+/* reference include/spark/kernels.h:384-385 (w4_quantize_bf16). W bf16 [K][N]; qweight int32
+ * [K/8][N] (GPTQ order); scales bf16 [K/128][N]; zeros u8 [K/128][N] or NULL (symmetric).
+ * K % 128 == 0, N % 16 == 0. */
+SPK_API int spk_w4_quantize_bf16(const void* W, int32_t* qweight, void* scales, uint8_t* zeros,
+                                 int K, int N, void* stream);
+/* reference include/spark/kernels.h:390 (w4_repack): qweight -> int32 [N/16][K/64][32][4].
+ * K % 64 == 0, N % 16 == 0. */
+SPK_API int spk_w4_repack(const int32_t* qweight, int32_t* packed, int K, int N, void* stream);
+/* reference include/spark/kernels.h:411-413 (w4gemm_bf16): C bf16 [M][N] = A bf16 [M][K] times
+ * bf16((q - z) * s). N % 16 == 0, K % 128 == 0, M >= 1, 16-byte aligned A, packed, scales,
+ * zeros. variant 0 naive, 1 warp per strip, 2 tuned (default), 3 batch invariant. */
+SPK_API int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void* scales,
+                            const uint8_t* zeros, void* C, int M, int N, int K, int variant,
+                            void* stream);
+/* reference include/spark/kernels.h:414-416 */
+SPK_API int spk_w4gemm_num_variants(void);
+SPK_API int spk_w4gemm_default_variant(void);
+SPK_API int spk_w4gemm_supports(int M, int N, int K, int variant);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPK_H_ */

@@ -1,0 +1,171 @@
+"""GPU parity of the W4A16 path (quantizer, repack, GEMM variants) against the CPU oracle and
+the committed golden vectors. Mirrors the cases of the reference's tests/test_w4gemm.py."""
+
+import numpy as np
+import pytest
+import torch
+
+from tests.parity import assert_bf16_close, bf16_from_bits, seeded_acts, seeded_weight, t2n
+
+pytestmark = pytest.mark.gpu
+
+# (K, N): smallest legal, a single wide strip set, K with 3 and 9 groups (ragged ring), o-proj
+WEIGHTS = [(128, 16), (256, 48), (384, 4096), (1152, 256), (4096, 4096)]
+MS = [1, 3, 8, 9, 16, 17, 33, 64, 100, 256]
+
+
+@pytest.mark.parametrize("asym", [False, True], ids=["sym", "asym"])
+@pytest.mark.parametrize("shape", WEIGHTS, ids=lambda s: f"K{s[0]}_N{s[1]}")
+def test_w4_quantize_matches_oracle(sk, orc, shape, asym):
+    K, N = shape
+    w = seeded_weight(K, N)
+    w[:128, :16] = 0  # an all-zero group: scale 0, every code the zero point
+    qweight, scales, zeros = sk.w4_quantize(w.cuda(), asym=asym)
+    q_ref, s_ref, z_ref = orc.w4_quantize(t2n(w), asym=asym)
+    assert qweight.shape == (K // 8, N) and qweight.dtype == torch.int32
+    assert scales.shape == (K // 128, N) and scales.dtype == torch.bfloat16
+    assert np.array_equal(t2n(qweight), q_ref)
+    assert np.array_equal(t2n(scales), s_ref)
+    if asym:
+        assert np.array_equal(t2n(zeros), z_ref)
+    else:
+        assert zeros is None
+
+
+@pytest.mark.parametrize("tag", ["sym", "asym"])
+def test_w4_quantize_and_repack_golden(sk, golden, tag):
+    g = golden("w4")
+    w = bf16_from_bits(g["w"])
+    qweight, scales, zeros = sk.w4_quantize(w, asym=tag == "asym")
+    assert np.array_equal(t2n(qweight), g[f"{tag}_qweight"])
+    assert np.array_equal(t2n(scales), g[f"{tag}_scales"])
+    if tag == "asym":
+        assert np.array_equal(t2n(zeros), g["asym_zeros"])
+    assert np.array_equal(t2n(sk.w4_repack(qweight)), g[f"{tag}_packed"])
+
+
+@pytest.mark.parametrize("shape", WEIGHTS, ids=lambda s: f"K{s[0]}_N{s[1]}")
+def test_w4_repack_matches_oracle(sk, orc, shape):
+    K, N = shape
+    g = torch.Generator(device="cpu").manual_seed(K + N)
+    q = torch.randint(0, 16, (K, N), dtype=torch.uint8, generator=g)
+    qweight = orc.w4_pack_gptq(q.numpy())
+    packed = sk.w4_repack(torch.from_numpy(qweight).cuda())
+    assert packed.shape == (N // 16, 2 * K) and packed.dtype == torch.int32
+    assert np.array_equal(t2n(packed), orc.w4_repack(qweight))
+    assert np.array_equal(orc.w4_unpack(t2n(packed)), q.numpy())
+
+
+def _case(sk, orc, M, K, N, variant, asym=False, reps=1):
+    w = seeded_weight(K, N, seed=K + N)
+    a = seeded_acts(M, K, seed=M)
+    ww = sk.W4Weight.quantize(w.cuda(), asym=asym)
+    want = orc.w4gemm(t2n(a), t2n(ww.packed), t2n(ww.scales), t2n(ww.zeros))
+    for _ in range(reps):
+        got = sk.w4gemm(a.cuda(), ww, variant=variant)
+        assert got.shape == (M, N) and got.dtype == torch.bfloat16
+        assert_bf16_close(got, want, f"w4gemm v{variant} M={M} K={K} N={N}")
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("M", MS)
+@pytest.mark.parametrize("shape", WEIGHTS, ids=lambda s: f"K{s[0]}_N{s[1]}")
+def test_w4gemm_matches_oracle(sk, orc, shape, M, variant):
+    K, N = shape
+    if variant == 0 and M * N * K > 2 ** 28:
+        pytest.skip("the naive rung is only checked on the small shapes")
+    if K * N >= 4096 * 4096 and M > 64:
+        pytest.skip("oracle time: the large weight is covered at M <= 64 and by the Llama shapes")
+    # three calls on variant 2: the split-K scratch and its counters are left zeroed
+    _case(sk, orc, M, K, N, variant, reps=3 if variant == 2 else 1)
+
+
+@pytest.mark.parametrize("M", [1, 16, 64, 100])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+def test_w4gemm_asymmetric(sk, orc, M, variant):
+    _case(sk, orc, M, 1152, 256, variant, asym=True)
+    if variant > 0 and M <= 64:
+        _case(sk, orc, M, 4096, 4096, variant, asym=True)
+
+
+LLAMA = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]
+
+
+@pytest.mark.parametrize("M", [1, 16, 64])
+@pytest.mark.parametrize("shape", LLAMA, ids=lambda s: f"K{s[0]}_N{s[1]}")
+def test_w4gemm_llama_shapes(sk, orc, shape, M):
+    K, N = shape
+    _case(sk, orc, M, K, N, -1, reps=2)
+
+
+def test_w4gemm_weight_bits_are_the_oracle(sk, orc):
+    """One-hot activations return the dequantized weight itself, bit for bit, on every variant."""
+    K, N = 256, 64
+    w = seeded_weight(K, N)
+    ww = sk.W4Weight.quantize(w.cuda(), asym=True)
+    deq = orc.w4_dequantize(t2n(ww.packed), t2n(ww.scales), t2n(ww.zeros))
+    a = torch.eye(K, dtype=torch.bfloat16, device="cuda")
+    for v in range(sk.num_variants("w4gemm")):
+        assert np.array_equal(t2n(sk.w4gemm(a, ww, variant=v)), deq), v
+
+
+def test_w4gemm_golden(sk, golden):
+    g = golden("w4")
+    for tag in ("sym", "asym"):
+        z = torch.from_numpy(g["asym_zeros"]).cuda() if tag == "asym" else None
+        packed = torch.from_numpy(g[f"{tag}_packed"]).cuda()
+        scales = bf16_from_bits(g[f"{tag}_scales"])
+        a = bf16_from_bits(g["a"])
+        for v in range(4):
+            assert_bf16_close(sk.w4gemm(a, packed, scales, z, variant=v), g[f"{tag}_c"], f"golden {tag} v{v}")
+
+
+def test_w4gemm_batch_invariant_rows(sk):
+    """Variant 3: row i of C has the same bits whatever M is and wherever it sits in the batch."""
+    K, N = 1152, 256
+    ww = sk.W4Weight.quantize(seeded_weight(K, N).cuda())
+    a = seeded_acts(130, K).cuda()
+    full = sk.w4gemm(a, ww, variant=3)
+    for M in (1, 3, 8, 9, 16, 17, 33, 64, 65, 129):
+        assert torch.equal(sk.w4gemm(a[:M].contiguous(), ww, variant=3), full[:M]), M
+    assert torch.equal(sk.w4gemm(a[5:6].contiguous(), ww, variant=3), full[5:6])
+
+
+def test_w4gemm_rejects_bad_input(sk):
+    w = seeded_weight(256, 64).cuda()
+    ww = sk.W4Weight.quantize(w)
+    a = torch.randn(4, 256, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        sk.w4gemm(a[:, :128].contiguous(), ww)  # K mismatch
+    with pytest.raises(RuntimeError):
+        sk.w4gemm(a.float(), ww)  # not bf16
+    with pytest.raises(RuntimeError):
+        sk.w4_quantize(torch.randn(200, 64, device="cuda", dtype=torch.bfloat16))  # K % 128
+    with pytest.raises(RuntimeError):
+        sk.w4gemm(a, ww, variant=sk.num_variants("w4gemm"))
+    assert ww.shape == (256, 64)
+
+
+def test_w4gemm_in_a_cuda_graph(sk, orc):
+    """The default variant captured in a CUDA graph replays correctly (scratch allocated before
+    capture, left clean by every launch)."""
+    K, N, M = 4096, 4096, 16
+    ww = sk.W4Weight.quantize(seeded_weight(K, N).cuda())
+    a = seeded_acts(M, K).cuda()
+    sk._C.init()
+    want = orc.w4gemm(t2n(a), t2n(ww.packed), t2n(ww.scales), None)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sk.w4gemm(a, ww, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sk.w4gemm(a, ww, out=out)
+    for _ in range(3):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert_bf16_close(out, want, "graph replay")
+    assert sk._C.device_status() == 0
