@@ -34,6 +34,8 @@ using ptx::mbar_arrive_expect_tx;
 using ptx::mbar_init;
 using ptx::mbar_wait;
 
+__host__ __device__ constexpr int cdiv_c(int a, int b) { return (a + b - 1) / b; }
+
 // ---- variant 0 ----------------------------------------------------------------------------------
 
 __global__ void w4_naive_kernel(const __nv_bfloat16* __restrict__ A, const uint32_t* __restrict__ packed,
@@ -64,23 +66,22 @@ struct ActGroup {
     uint4 v[4];
 };
 
+// Rows past M re-read row M - 1: an MMA column only ever feeds its own output column, and the
+// stores skip tok >= M, so the duplicate is never seen; this keeps the load free of divergence.
 __device__ __forceinline__ ActGroup load_acts(const __nv_bfloat16* __restrict__ A, int tok, int M, int K, int g,
                                               int c) {
     ActGroup a;
-    if (tok < M) {
-        const __nv_bfloat16* p = A + static_cast<size_t>(tok) * K + g * w4::kGroup + 8 * c;
+    tok = tok < M ? tok : M - 1;
+    const __nv_bfloat16* p = A + static_cast<size_t>(tok) * K + g * w4::kGroup + 8 * c;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a.v[i] = ptx::ldg_cached(p + 32 * i);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a.v[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
+    for (int i = 0; i < 4; ++i) a.v[i] = ptx::ldg_cached(p + 32 * i);
     return a;
 }
 
-// One 64-k unit (a lane's uint4 of four words) of one strip against MT token tiles.
-template <int MT>
-__device__ __forceinline__ void unit_mma(float (&acc)[MT][4], const uint4& q, int half, uint32_t off_lo,
+// One 64-k unit (a lane's uint4 of four words) of one strip against MT token tiles. NA = 2
+// alternates two accumulators over the k16 steps so consecutive MMAs do not depend on each other.
+template <int MT, int NA>
+__device__ __forceinline__ void unit_mma(float (&acc)[MT][NA][4], const uint4& q, int half, uint32_t off_lo,
                                          uint32_t off_hi, uint32_t s_lo, uint32_t s_hi,
                                          const ActGroup (&act)[MT]) {
     const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
@@ -92,9 +93,9 @@ __device__ __forceinline__ void unit_mma(float (&acc)[MT][4], const uint4& q, in
         for (int mt = 0; mt < MT; ++mt) {
             const uint4& a = act[mt].v[2 * half + (j >> 1)];
             if (j & 1)
-                ptx::mma_bf16_16816(acc[mt], x, a.z, a.w);
+                ptx::mma_bf16_16816(acc[mt][j % NA], x, a.z, a.w);
             else
-                ptx::mma_bf16_16816(acc[mt], x, a.x, a.y);
+                ptx::mma_bf16_16816(acc[mt][j % NA], x, a.x, a.y);
         }
     }
 }
@@ -126,7 +127,7 @@ w4_strip_kernel(const __nv_bfloat16* __restrict__ A, const uint4* __restrict__ p
     const uint4* wp = packed + static_cast<size_t>(t) * G * 64 + lane;
     const unsigned short* sp = reinterpret_cast<const unsigned short*>(scales) + 16 * t + gl;
     const uint8_t* zp = zeros + 16 * t + gl;
-    float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+    float acc[1][1][4] = {{{0.f, 0.f, 0.f, 0.f}}};
     for (int g = 0; g < G; ++g) {
         ActGroup act[1] = {load_acts(A, tok0 + gl, M, K, g, c)};
         const uint4 q0 = ptx::ldg_stream(wp + (2 * g) * 32), q1 = ptx::ldg_stream(wp + (2 * g + 1) * 32);
@@ -137,13 +138,32 @@ w4_strip_kernel(const __nv_bfloat16* __restrict__ A, const uint4* __restrict__ p
             o_lo = w4::offset_pair(zp[static_cast<size_t>(g) * N]);
             o_hi = w4::offset_pair(zp[static_cast<size_t>(g) * N + 8]);
         }
-        unit_mma<1>(acc, q0, 0, o_lo, o_hi, s_lo, s_hi, act);
-        unit_mma<1>(acc, q1, 1, o_lo, o_hi, s_lo, s_hi, act);
+        unit_mma<1, 1>(acc, q0, 0, o_lo, o_hi, s_lo, s_hi, act);
+        unit_mma<1, 1>(acc, q1, 1, o_lo, o_hi, s_lo, s_hi, act);
     }
-    store_tile(C, acc[0], tok0, M, N, 16 * t, lane);
+    store_tile(C, acc[0][0], tok0, M, N, 16 * t, lane);
 }
 
 // ---- variants 2 and 3: the weight stream ------------------------------------------------------------
+//
+// Work decomposition. A super-strip is kStreamWarps * NS strips (128 * NS columns); a chunk is CG
+// groups of one super-strip. Chunks are numbered super-strip major and every CTA takes an equal
+// contiguous range of them, so every SM streams and dequantizes the same amount whatever the
+// shape (the kernel is bound by the ALU pipes as much as by HBM, so balance matters). Warp w
+// owns strips (super * 8 + w) * NS .. + NS - 1 of each super-strip the range touches.
+// A K segment that covers a whole strip goes straight to C. A partial one is added to an fp32
+// scratch with fire-and-forget reductions; at the very end of the warp one fence publishes them,
+// a per-strip counter is advanced, and whoever completes a strip converts it to bf16 and leaves
+// scratch and counter zeroed. Variant 3 cuts the ranges at super-strip boundaries instead: no
+// scratch, a fixed summation order.
+//
+// Data movement per warp, private to the warp (no block-level barrier anywhere in the loop):
+//   codes   one bulk asynchronous copy (TMA engine, untiled) per strip per chunk: CG KiB,
+//           contiguous in the repacked layout (2 KiB or more per request: smaller requests
+//           measured well below the HBM rate)
+//   scales  16-byte cp.async copies (one per half row of 16 bf16), zero points likewise
+// all landing in ring slot (chunk % ST) and all signalled on that slot's mbarrier: the bulk copy
+// through its transaction count, the cp.async copies through one deferred arrive per lane.
 
 constexpr int kStreamWarps = 8;  // warps per CTA, one strip set each, along N
 
@@ -154,269 +174,455 @@ struct StreamParams {
     const unsigned char* zeros;   // u8 [G][N] or null
     __nv_bfloat16* C;
     int M, N, K, G, T;
-    int super_strips;       // cdiv(T, kStreamWarps * NS)
-    long long total_units;  // super_strips * G
-    int whole;              // CTA ranges end on super-strip boundaries (no shared strips)
-    float* partials;        // fp32 [M][N] scratch, zero on entry and on exit
-    unsigned* counters;     // [gridDim.y][T], zero on entry and on exit
+    int whole;           // 1: CTA ranges end on super-strip boundaries (no scratch, fixed order)
+    int super_strips;    // cdiv(T, kStreamWarps * NS)
+    int rows_max;        // min(M, 8 MT): token rows the activation ring is sized for
+    float* partials;     // fp32 [M][N] scratch, zero on entry and on exit
+    unsigned* counters;  // [gridDim.y][T], zero on entry and on exit
     int* status;
 };
 
-// Bytes of one ring slot of one warp.
-template <int NS, bool ASYM>
+template <int NS, int CG, bool ASYM>
 struct Slot {
-    static constexpr int kCodes = NS * w4::kGroupBytes;
-    static constexpr int kScales = NS * 32;
-    static constexpr int kZeros = ASYM ? NS * 16 : 0;
+    static constexpr int kCodes = NS * CG * w4::kGroupBytes;
+    static constexpr int kScales = NS * CG * 32;
+    static constexpr int kZeros = ASYM ? NS * CG * 16 : 0;
     static constexpr int kBytes = kCodes + kScales + kZeros;
 };
 
-template <int MT, int NS, int ST, bool ASYM>
-constexpr int stream_smem_bytes() {
-    return kStreamWarps * (ST * Slot<NS, ASYM>::kBytes + ST * 8);
+// Activation ring (shared by the CTA): stage j holds, for every token row of this CTA's chunk of
+// tokens, the CG * 128 activations of chunk j. One extra warp streams it with one bulk copy per
+// row; the eight consumer warps read their MMA B operands from it with LDS.128. Activations must
+// live in shared memory: the codes stream through L2 at the HBM rate, and activation loads that
+// miss the small L1 left beside ~200 KiB of shared memory then queue behind that stream
+// (measured: 25% L1 misses doubled the kernel time).
+template <int MT>
+struct ActRing {
+    static constexpr int kStages = MT <= 2 ? 8 : (MT == 4 ? 4 : 2);  // 8 MT rows x (CG x 256 + 64) bytes per stage
+};
+// Row pitch: chunk bytes + 64, so that the eight lanes of a quarter warp (two token rows x four
+// 16-byte columns) fall into distinct 16-byte bank groups.
+__host__ __device__ constexpr int act_pitch(int cg) { return cg * 256 + 64; }
+
+template <int AST, int NS, int CG, int ST, bool ASYM>
+constexpr int stream_smem_bytes(int rows) {
+    return kStreamWarps * ST * Slot<NS, CG, ASYM>::kBytes + AST * rows * (CG * 256 + 64) +
+           (2 * AST + kStreamWarps * ST) * 8;
 }
 
-template <int MT, int NS, int ST, bool ASYM>
-__global__ void __launch_bounds__(kStreamWarps * 32)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(dst)), "l"(src) : "memory");
+}
+// Arrive on `bar` once every cp.async this thread issued so far has landed (the arrival is
+// already part of the barrier's expected count).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(ptx::smem_u32(bar)) : "memory");
+}
+
+// Resident CTAs the register budget is held to: the loop is bound by instruction issue and two
+// half-rate pipes, and needs six to eight warps per scheduler to keep them busy.
+#ifndef SPK_W4_MINCTAS
+#define SPK_W4_MINCTAS 1
+#endif
+template <int MT, int NS>
+struct StreamOcc {
+    static constexpr int kMinCtas = SPK_W4_MINCTAS;
+};
+
+template <int MT, int NS, int CG, int ST, bool ASYM, bool DUAL>
+__global__ void __launch_bounds__(kStreamWarps * 32, StreamOcc<MT, NS>::kMinCtas)
 w4_stream_kernel(const StreamParams p) {
-    using S = Slot<NS, ASYM>;
+    using S = Slot<NS, CG, ASYM>;
+    constexpr int NA = DUAL ? 2 : 1;
+    constexpr int kPitch = act_pitch(CG);
+    constexpr int kActStages = ActRing<MT>::kStages;
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gl = lane >> 2, c = lane & 3;
-    unsigned char* ring = smem + warp * (ST * S::kBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStreamWarps * ST * S::kBytes) + warp * ST;
 
-    // This CTA's contiguous range of (super-strip, group) units.
-    long long f0, f1;
+    // This CTA's range [f0, f1) of chunks, numbered super-strip major (G % CG == 0).
+    const int chunks = p.G / CG;
+    int f0, f1;
     if (p.whole) {
-        f0 = static_cast<long long>(blockIdx.x) * p.super_strips / gridDim.x * p.G;
-        f1 = static_cast<long long>(blockIdx.x + 1) * p.super_strips / gridDim.x * p.G;
+        f0 = static_cast<int>(static_cast<long long>(blockIdx.x) * p.super_strips / gridDim.x) * chunks;
+        f1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.super_strips / gridDim.x) * chunks;
     } else {
-        f0 = blockIdx.x * p.total_units / gridDim.x;
-        f1 = (blockIdx.x + 1) * p.total_units / gridDim.x;
+        const long long total = static_cast<long long>(p.super_strips) * chunks;
+        f0 = static_cast<int>(blockIdx.x * total / gridDim.x);
+        f1 = static_cast<int>((blockIdx.x + 1) * total / gridDim.x);
     }
-    const int n_units = static_cast<int>(f1 - f0);
-    if (n_units <= 0) return;
+    const int n_chunks = f1 - f0;
+    const int ss0 = f0 / chunks, ch0 = f0 - ss0 * chunks;
     const int tok0 = blockIdx.y * (8 * MT);
+    int rows = p.M - tok0;  // token rows this CTA really has
+    rows = rows > 8 * MT ? 8 * MT : rows;
 
-    if (lane == 0) {
+    // shared memory: [8 warps][ST slots] codes+scales(+zeros) | act ring | barriers
+    unsigned char* act_ring = smem + kStreamWarps * ST * S::kBytes;
+    const int act_stage = p.rows_max * kPitch;
+    uint64_t* bar_base = reinterpret_cast<uint64_t*>(act_ring + kActStages * (p.rows_max * kPitch));
+    uint64_t* a_full = bar_base;
+    uint64_t* a_empty = bar_base + kActStages;
+    uint64_t* bars = bar_base + 2 * kActStages + warp * ST;  // this warp's code ring (consumers only)
+
+    if (threadIdx.x == 0) {
 #pragma unroll
-        for (int s = 0; s < ST; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < kActStages; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], kStreamWarps);
+        }
         ptx::fence_mbar_init();
     }
-    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < ST; ++s) mbar_init(&bars[s], 33);  // 1 expect_tx arrive + 32 cp.async arrives
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();  // the only block-wide barrier: barrier objects are ready
+    if (n_chunks <= 0) return;
 
-    // Lane 0 arms slot (i % ST) with unit i: per strip of this warp one 1 KiB bulk copy of codes,
-    // 32 bytes of scales and, with zero points, 16 bytes of zeros.
-    auto issue = [&](int i) {
-        const long long f = f0 + i;
-        const int ts = static_cast<int>(f / p.G);
-        const int g = static_cast<int>(f - static_cast<long long>(ts) * p.G);
-        unsigned char* slot = ring + (i % ST) * S::kBytes;
-        uint64_t* bar = &bars[i % ST];
-        const int t_first = (ts * kStreamWarps + warp) * NS;
-        int valid = p.T - t_first;
-        valid = valid < 0 ? 0 : (valid > NS ? NS : valid);
-        if (valid == 0) {
-            mbar_arrive(bar);
-            return;
-        }
-        mbar_arrive_expect_tx(bar, valid * (w4::kGroupBytes + 32 + (ASYM ? 16 : 0)));
-        for (int s = 0; s < valid; ++s) {
-            const int t = t_first + s;
-            bulk_g2s(slot + s * w4::kGroupBytes,
-                     p.packed + (static_cast<size_t>(t) * p.G + g) * w4::kGroupBytes, w4::kGroupBytes, bar);
-            bulk_g2s(slot + S::kCodes + s * 32, p.scales + (static_cast<size_t>(g) * p.N + 16 * t) * 2, 32, bar);
-            if (ASYM)
-                bulk_g2s(slot + S::kCodes + S::kScales + s * 16, p.zeros + static_cast<size_t>(g) * p.N + 16 * t,
-                         16, bar);
+    // ---- activation producer state (warp 0 only): chunk j goes to stage j % kActStages, one bulk
+    // copy per token row issued by lane r. It runs kActLead chunks ahead of warp 0's own
+    // consumption, which leaves the other warps kActStages - kActLead chunks of slack before
+    // warp 0 would have to wait for them.
+    constexpr int kActLead = kActStages > 4 ? kActStages - 3 : kActStages - 1;
+    const unsigned char* a_row = reinterpret_cast<const unsigned char*>(p.A) +
+                                 static_cast<size_t>(tok0 + (lane < rows ? lane : 0)) * p.K * 2;
+    int a_issued = 0, a_ch = ch0, a_pstage = 0;
+    unsigned a_pphase = 0;
+    bool a_ok = true;
+    auto issue_acts = [&](int upto) {  // warp 0, all lanes
+        while (a_issued < upto && a_ok) {
+            if (a_issued >= kActStages) {
+                a_ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[a_pstage], a_pphase ^ 1u, p.status));
+                if (!a_ok) break;
+            }
+            if (lane == 0) mbar_arrive_expect_tx(&a_full[a_pstage], rows * (CG * 256));
+            __syncwarp();
+            for (int r = lane; r < rows; r += 32)
+                bulk_g2s(act_ring + a_pstage * act_stage + r * kPitch,
+                         a_row + static_cast<size_t>(r - lane) * p.K * 2 + static_cast<size_t>(a_ch) * (CG * 256),
+                         CG * 256, &a_full[a_pstage]);
+            a_ch = a_ch + 1 == chunks ? 0 : a_ch + 1;
+            ++a_issued;
+            if (++a_pstage == kActStages) {
+                a_pstage = 0;
+                a_pphase ^= 1u;
+            }
         }
     };
+    if (warp == 0) issue_acts(n_chunks < kActLead ? n_chunks : kActLead);
 
-    if (lane == 0) {
-        const int pre = n_units < ST ? n_units : ST;
-        for (int i = 0; i < pre; ++i) issue(i);
-    }
+    unsigned char* ring = smem + warp * (ST * S::kBytes);
+    const size_t strip_bytes = static_cast<size_t>(p.G) * w4::kGroupBytes;
+    auto valid_of = [&](int t_first) {
+        int v = p.T - t_first;
+        return v < 0 ? 0 : (v > NS ? NS : v);
+    };
 
-    int ts = static_cast<int>(f0 / p.G);
-    int g = static_cast<int>(f0 - static_cast<long long>(ts) * p.G);
-    int seg_g0 = g;  // first group of the segment being accumulated
-    float acc[NS][MT][4];
+    // ---- code producer (warp-collective; runs ST chunks ahead of the consumer) ----
+    // lane roles for the small copies: half a scale row (row = strip s x group gi), a zero-point row
+    const int sc_row = lane >> 1, sc_s = sc_row / CG, z_s = lane / CG;
+    int p_left = n_chunks, p_slot = 0, p_ch = ch0;
+    int p_t = (ss0 * kStreamWarps + warp) * NS, p_valid = valid_of(p_t);
+    const unsigned char* code_src = p.packed + static_cast<size_t>(p_t) * strip_bytes +
+                                    static_cast<size_t>(ch0) * (CG * w4::kGroupBytes);
+    const unsigned char* sc_src =
+        p.scales + (static_cast<size_t>(ch0 * CG + sc_row % CG) * p.N + 16 * (p_t + sc_s)) * 2 + (lane & 1) * 16;
+    const unsigned char* z_src =
+        ASYM ? p.zeros + static_cast<size_t>(ch0 * CG + lane % CG) * p.N + 16 * (p_t + z_s) : nullptr;
+    const size_t sc_step = static_cast<size_t>(CG) * p.N * 2, z_step = static_cast<size_t>(CG) * p.N;
+    auto issue = [&]() {
+        if (p_left <= 0) return;
+        unsigned char* slot = ring + p_slot * S::kBytes;
+        uint64_t* bar = &bars[p_slot];
+        if (lane == 0) {
+            if (p_valid == 0) {
+                mbar_arrive(bar);
+            } else {
+                mbar_arrive_expect_tx(bar, p_valid * (CG * w4::kGroupBytes));
+#pragma unroll
+                for (int s = 0; s < NS; ++s)
+                    if (s < p_valid)
+                        bulk_g2s(slot + s * (CG * w4::kGroupBytes), code_src + s * strip_bytes, CG * w4::kGroupBytes, bar);
+            }
+        }
+        if (sc_row < NS * CG && sc_s < p_valid) cp_async16(slot + S::kCodes + lane * 16, sc_src);
+        if (ASYM && lane < NS * CG && z_s < p_valid) cp_async16(slot + S::kCodes + S::kScales + lane * 16, z_src);
+        cp_async_arrive(bar);
+        --p_left;
+        p_slot = p_slot + 1 == ST ? 0 : p_slot + 1;
+        if (++p_ch == chunks) {
+            // next super-strip: same warp, strips 8 NS further on, K back to 0
+            p_ch = 0;
+            p_t += kStreamWarps * NS;
+            p_valid = valid_of(p_t);
+            code_src += CG * w4::kGroupBytes + (kStreamWarps * NS - 1) * strip_bytes;
+            sc_src += sc_step + kStreamWarps * NS * 32 - static_cast<size_t>(p.G) * p.N * 2;
+            if (ASYM) z_src += z_step + kStreamWarps * NS * 16 - static_cast<size_t>(p.G) * p.N;
+        } else {
+            code_src += CG * w4::kGroupBytes;
+            sc_src += sc_step;
+            if (ASYM) z_src += z_step;
+        }
+    };
+#pragma unroll 1
+    for (int s = 0; s < ST; ++s) issue();
+
+    // ---- consumer ----
+    float acc[NS][MT][NA][4];
 #pragma unroll
     for (int s = 0; s < NS; ++s)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[s][mt][e] = 0.f;
+            for (int a = 0; a < NA; ++a)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[s][mt][a][e] = 0.f;
 
-    // Ends the segment [seg_g0, g] of super-strip ts: a whole K goes straight to C, a part of K
-    // goes through the scratch, and whoever completes the strip converts it.
-    auto flush = [&](int ts_, int g_last) {
-        const bool whole_k = seg_g0 == 0 && g_last == p.G - 1;
+    // this lane's activation rows (token tiles mt); rows past the CTA's last re-read that one
+    int act_off[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        int r = 8 * mt + gl;
+        r = r < rows ? r : rows - 1;
+        act_off[mt] = r * kPitch + 16 * c;
+    }
+
+    // Partial K segments this warp has added to the scratch: at most the first and the last of
+    // its range. (first strip, chunks added); completed at the end of the kernel.
+    int pend_t[2] = {0, 0}, pend_n[2] = {0, 0}, n_pend = 0;
+
+    // Ends the K segment that began at chunk seg0 of the strips at t_first and ends before ch_end.
+    auto flush = [&](int t_first, int seg0, int ch_end) {
+        const int valid = valid_of(t_first);
+        const bool whole_k = seg0 == 0 && ch_end == chunks;
 #pragma unroll
         for (int s = 0; s < NS; ++s) {
-            const int t = (ts_ * kStreamWarps + warp) * NS + s;
-            if (t < p.T) {
-                if (whole_k) {
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) store_tile(p.C, acc[s][mt], tok0 + 8 * mt, p.M, p.N, 16 * t, lane);
-                } else {
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int tok = tok0 + 8 * mt + 2 * c + (e & 1);
-                            const int n = 16 * t + gl + 8 * (e >> 1);
-                            if (tok < p.M) atomicAdd(p.partials + static_cast<size_t>(tok) * p.N + n, acc[s][mt][e]);
-                        }
-                    __threadfence();
-                    __syncwarp();
-                    unsigned done = 0;
-                    if (lane == 0)
-                        done = atomicAdd(p.counters + static_cast<size_t>(blockIdx.y) * p.T + t,
-                                         static_cast<unsigned>(g_last - seg_g0 + 1));
-                    done = __shfl_sync(0xffffffffu, done, 0);
-                    if (done + static_cast<unsigned>(g_last - seg_g0 + 1) == static_cast<unsigned>(p.G)) {
-                        __threadfence();
-#pragma unroll
-                        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int tok = tok0 + 8 * mt + 2 * c + (e & 1);
-                                const int n = 16 * t + gl + 8 * (e >> 1);
-                                if (tok < p.M) {
-                                    float* cell = p.partials + static_cast<size_t>(tok) * p.N + n;
-                                    p.C[static_cast<size_t>(tok) * p.N + n] = __float2bfloat16_rn(__ldcg(cell));
-                                    __stcg(cell, 0.f);
-                                }
-                            }
-                        if (lane == 0) p.counters[static_cast<size_t>(blockIdx.y) * p.T + t] = 0u;
-                    }
-                }
-            }
+            float v[MT][4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[s][mt][e] = 0.f;
-        }
-        seg_g0 = 0;
-    };
-
-    bool ok = true;
-    for (int i = 0; i < n_units; ++i) {
-        // activations first: their latency overlaps the wait on the ring
-        ActGroup act[MT];
+                for (int e = 0; e < 4; ++e) {
+                    v[mt][e] = DUAL ? acc[s][mt][0][e] + acc[s][mt][NA - 1][e] : acc[s][mt][0][e];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) act[mt] = load_acts(p.A, tok0 + 8 * mt + gl, p.M, p.K, g, c);
-
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars[i % ST], (i / ST) & 1, p.status));
-        if (!ok) {
-            // Drain: give the copies already issued a bounded chance to land, then leave.
-            for (int j = i + 1; j < n_units && j < i + ST; ++j) (void)mbar_wait(&bars[j % ST], (j / ST) & 1, nullptr);
-            break;
-        }
-        const unsigned char* slot = ring + (i % ST) * S::kBytes;
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const int t = (ts * kStreamWarps + warp) * NS + s;
-            if (t < p.T) {
-                const unsigned short* sc = reinterpret_cast<const unsigned short*>(slot + S::kCodes + s * 32);
-                const uint32_t s_lo = w4::splat16(sc[gl]), s_hi = w4::splat16(sc[gl + 8]);
-                uint32_t o_lo = w4::kSymOffset, o_hi = w4::kSymOffset;
-                if (ASYM) {
-                    const unsigned char* zp = slot + S::kCodes + S::kScales + s * 16;
-                    o_lo = w4::offset_pair(zp[gl]);
-                    o_hi = w4::offset_pair(zp[gl + 8]);
+                    for (int a = 0; a < NA; ++a) acc[s][mt][a][e] = 0.f;
                 }
-                const uint4* codes = reinterpret_cast<const uint4*>(slot + s * w4::kGroupBytes);
-                const uint4 q0 = codes[lane], q1 = codes[32 + lane];
-                unit_mma<MT>(acc[s], q0, 0, o_lo, o_hi, s_lo, s_hi, act);
-                unit_mma<MT>(acc[s], q1, 1, o_lo, o_hi, s_lo, s_hi, act);
+            if (s >= valid) continue;
+            const int t = t_first + s;
+            if (whole_k) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) store_tile(p.C, v[mt], tok0 + 8 * mt, p.M, p.N, 16 * t, lane);
+            } else {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = tok0 + 8 * mt + 2 * c + (e & 1);
+                        const int n = 16 * t + gl + 8 * (e >> 1);
+                        if (tok < p.M) atomicAdd(p.partials + static_cast<size_t>(tok) * p.N + n, v[mt][e]);
+                    }
             }
         }
-        __syncwarp();  // every lane has consumed the slot before it is re-armed
-        if (lane == 0 && i + ST < n_units) issue(i + ST);
+        if (!whole_k && valid > 0) {
+            pend_t[n_pend] = t_first;
+            pend_n[n_pend] = ch_end - seg0;
+            ++n_pend;
+        }
+    };
 
-        if (g == p.G - 1 || i == n_units - 1) {
-            flush(ts, g);
-            g = (g == p.G - 1) ? 0 : g + 1;
-            ts += (g == 0);
-        } else {
-            ++g;
+    int slot_i = 0, a_stage = 0, ch = ch0, seg0 = ch0;
+    int t_first = (ss0 * kStreamWarps + warp) * NS, valid = valid_of(t_first);
+    unsigned phase = 0, a_phase = 0;
+    for (int left = n_chunks; left > 0; --left) {
+        bool ok = mbar_wait(&a_full[a_stage], a_phase, p.status);
+        ok = __all_sync(0xffffffffu, ok && mbar_wait(&bars[slot_i], phase, p.status));
+        if (!ok) {
+            // Drain: give the copies already issued a bounded chance to land, then leave.
+            for (int j = 1; j < ST; ++j) {
+                const int sj = (slot_i + j) % ST;
+                (void)mbar_wait(&bars[sj], sj > slot_i ? phase : phase ^ 1u, nullptr);
+            }
+            return;
+        }
+        const unsigned char* slot = ring + slot_i * S::kBytes;
+        const unsigned char* acts = act_ring + a_stage * act_stage;
+#pragma unroll
+        for (int gi = 0; gi < CG; ++gi) {
+            ActGroup act[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    act[mt].v[i] = *reinterpret_cast<const uint4*>(acts + act_off[mt] + gi * 256 + i * 64);
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                if (s < valid) {
+                    const unsigned short* sc =
+                        reinterpret_cast<const unsigned short*>(slot + S::kCodes + (s * CG + gi) * 32);
+                    const uint32_t s_lo = w4::splat16(sc[gl]), s_hi = w4::splat16(sc[gl + 8]);
+                    uint32_t o_lo = w4::kSymOffset, o_hi = w4::kSymOffset;
+                    if (ASYM) {
+                        const unsigned char* zp = slot + S::kCodes + S::kScales + (s * CG + gi) * 16;
+                        o_lo = w4::offset_pair(zp[gl]);
+                        o_hi = w4::offset_pair(zp[gl + 8]);
+                    }
+                    const uint4* codes = reinterpret_cast<const uint4*>(slot + (s * CG + gi) * w4::kGroupBytes);
+                    const uint4 q0 = codes[lane], q1 = codes[32 + lane];
+                    unit_mma<MT, NA>(acc[s], q0, 0, o_lo, o_hi, s_lo, s_hi, act);
+                    unit_mma<MT, NA>(acc[s], q1, 1, o_lo, o_hi, s_lo, s_hi, act);
+                }
+            }
+        }
+        __syncwarp();  // every lane has consumed both slots before they are handed back
+        if (lane == 0) mbar_arrive(&a_empty[a_stage]);
+        issue();
+        if (warp == 0) {
+            const int consumed = n_chunks - left + 1;
+            issue_acts(consumed + kActLead < n_chunks ? consumed + kActLead : n_chunks);
+        }
+        if (++slot_i == ST) {
+            slot_i = 0;
+            phase ^= 1u;
+        }
+        if (++a_stage == kActStages) {
+            a_stage = 0;
+            a_phase ^= 1u;
+        }
+        if (++ch == chunks || left == 1) {
+            flush(t_first, seg0, ch);
+            if (ch == chunks) {
+                ch = 0;
+                t_first += kStreamWarps * NS;
+                valid = valid_of(t_first);
+            }
+            seg0 = ch;
+        }
+    }
+
+    // ---- completion of the partial segments: one fence, then the per-strip counters ----
+    if (n_pend == 0) return;
+    __threadfence();
+    __syncwarp();
+    for (int i = 0; i < n_pend; ++i) {
+        const int nv = valid_of(pend_t[i]);
+        for (int s = 0; s < nv; ++s) {
+            const int t = pend_t[i] + s;
+            unsigned done = 0;
+            unsigned* counter = p.counters + static_cast<size_t>(blockIdx.y) * p.T + t;
+            if (lane == 0) done = atomicAdd(counter, static_cast<unsigned>(pend_n[i]));
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (done + static_cast<unsigned>(pend_n[i]) == static_cast<unsigned>(chunks)) {
+                __threadfence();
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = tok0 + 8 * mt + 2 * c + (e & 1);
+                        const int n = 16 * t + gl + 8 * (e >> 1);
+                        if (tok < p.M) {
+                            float* cell = p.partials + static_cast<size_t>(tok) * p.N + n;
+                            p.C[static_cast<size_t>(tok) * p.N + n] = __float2bfloat16_rn(__ldcg(cell));
+                            __stcg(cell, 0.f);
+                        }
+                    }
+                if (lane == 0) *counter = 0u;
+            }
         }
     }
 }
 
 // ---- host side --------------------------------------------------------------------------------------
 
-struct StreamShape {
-    int mt, ns, st;
-};
-
-// Environment override for sweeps: SPK_W4_CFG="mt,ns,st[,ctas_per_sm[,min_units]]".
+// Environment override for sweeps: SPK_W4_CFG="mt,ns,cg,st[,ctas_per_sm[,min_units]]" (0 = rule).
 struct StreamTuning {
-    int mt = 0, ns = 0, st = 0, ctas_per_sm = 0, min_units = 0;
+    int mt = 0, ns = 0, cg = 0, st = 0, ctas_per_sm = 0, min_units = 0;
 };
 
 StreamTuning read_tuning() {
     StreamTuning t;
     const char* e = std::getenv("SPK_W4_CFG");
-    if (e && *e) std::sscanf(e, "%d,%d,%d,%d,%d", &t.mt, &t.ns, &t.st, &t.ctas_per_sm, &t.min_units);
+    if (e && *e) std::sscanf(e, "%d,%d,%d,%d,%d,%d", &t.mt, &t.ns, &t.cg, &t.st, &t.ctas_per_sm, &t.min_units);
     return t;
 }
 
-template <int MT, int NS, int ST, bool ASYM>
-int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_cap, int min_units,
+template <int MT, int NS, int CG, int ST, bool ASYM, bool DUAL>
+int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target, int min_chunks,
                     const DeviceState& dev, cudaStream_t stream) {
     StreamParams p = base;
-    auto kernel = w4_stream_kernel<MT, NS, ST, ASYM>;
-    constexpr int smem = stream_smem_bytes<MT, NS, ST, ASYM>();
+    auto kernel = w4_stream_kernel<MT, NS, CG, ST, ASYM, DUAL>;
+    constexpr int smem_max = stream_smem_bytes<ActRing<MT>::kStages, NS, CG, ST, ASYM>(8 * MT);
     static bool configured[16] = {};
     if (!configured[dev.device & 15]) {
-        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
         configured[dev.device & 15] = true;
     }
-    int per_sm = 0;
-    SPK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kStreamWarps * 32, smem));
-    if (per_sm < 1) return fail(SPK_CUDA_ERROR, "w4gemm: stream kernel does not fit an SM (smem %d)", smem);
-    if (ctas_per_sm_cap > 0) per_sm = std::min(per_sm, ctas_per_sm_cap);
+    p.rows_max = std::min(p.M, 8 * MT);
+    const int smem = stream_smem_bytes<ActRing<MT>::kStages, NS, CG, ST, ASYM>(p.rows_max);
     p.super_strips = cdiv(p.T, kStreamWarps * NS);
-    p.total_units = static_cast<long long>(p.super_strips) * p.G;
+    const int chunks = p.G / CG;
     const int m_chunks = cdiv(p.M, 8 * MT);
-    // Partial strips need the scratch: fall back to whole strips when it does not cover [M][N].
+    // Shared strips need the scratch: whole strips when it does not cover [M][N].
     if (static_cast<int64_t>(p.M) * p.N > kPartialFloats || static_cast<int64_t>(m_chunks) * p.T > kCounters)
         whole = true;
     p.whole = whole ? 1 : 0;
-    const long long slots = static_cast<long long>(dev.sm_count) * per_sm;
-    // One CTA per `min_units` units at least (a unit is 8 KiB x NS of codes), at most what is
-    // resident at once; token chunks beyond the first share the slots.
-    const long long want = whole ? p.super_strips : std::max<long long>(1, p.total_units / std::max(1, min_units));
-    const long long ctas = std::min(want, std::max<long long>(1, slots / m_chunks));
-    const dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(m_chunks));
+    static int occupancy[16][8 * MT + 1] = {};  // per device and activation-ring height
+    int& occ = occupancy[dev.device & 15][p.rows_max];
+    if (occ == 0) {
+        SPK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kStreamWarps * 32, smem));
+        if (occ < 1) return fail(SPK_CUDA_ERROR, "w4gemm: stream kernel does not fit an SM (smem %d)", smem);
+    }
+    int per_sm = occ;
+    if (ctas_per_sm_target > 0) per_sm = std::min(per_sm, ctas_per_sm_target);
+    // Equal ranges over exactly the CTAs that are resident at once, but at least `min_chunks`
+    // chunks each; token chunks beyond the first share the slots.
+    const long long slots = std::max<long long>(1, static_cast<long long>(dev.sm_count) * per_sm / m_chunks);
+    const long long total = static_cast<long long>(p.super_strips) * chunks;
+    const long long want = whole ? p.super_strips : std::max<long long>(1, total / std::max(1, min_chunks));
+    const dim3 grid(static_cast<unsigned>(std::min(want, slots)), static_cast<unsigned>(m_chunks));
     kernel<<<grid, kStreamWarps * 32, smem, stream>>>(p);
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }
 
+// Block shapes, from sweeps on B200 (Llama-3-8B projections, CUDA-graph chained launches):
+//   M <= 8   one token tile, one strip per warp, 4-group chunks, 2 slots (8 KiB in flight per warp)
+//   M <= 16  two token tiles, same ring
+//   M <= 32 / 64  four / eight token tiles on 2-group chunks (registers); these two are the
+//            warp-level-MMA fallback for shapes the tcgen05 path does not take
+// SPK_W4_CFG="mt,ns,cg,st[,ctas_per_sm[,min_chunks]]" overrides the rule for sweeps (0 = rule);
+// only the shapes instantiated below exist.
 template <bool ASYM>
 int launch_stream(const StreamParams& p, bool whole, const DeviceState& dev, cudaStream_t stream) {
     static const StreamTuning tune = read_tuning();
     int mt = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
-    int ns = mt >= 2 ? 2 : 1;
-    if (tune.mt > 0 && (p.M <= 8 * tune.mt || tune.mt == 8)) mt = tune.mt;  // never fewer tiles than M needs per chunk
+    int ns = 1, cg = mt <= 2 ? 4 : 2;
+    if (tune.mt > 0 && (p.M <= 8 * tune.mt || tune.mt == 8)) mt = tune.mt;
     if (tune.ns > 0) ns = tune.ns;
-    if (mt == 8) ns = 1;  // 8 token tiles x 2 strips would spill
-    const int cap = tune.ctas_per_sm, min_units = tune.min_units > 0 ? tune.min_units : 2;
-#define SPK_W4_CASE(MT_, NS_, ST_)                                                       \
-    if (mt == MT_ && ns == NS_) return launch_stream_t<MT_, NS_, ST_, ASYM>(p, whole, cap, min_units, dev, stream)
-    SPK_W4_CASE(1, 1, 8);
-    SPK_W4_CASE(1, 2, 4);
-    SPK_W4_CASE(2, 1, 8);
-    SPK_W4_CASE(2, 2, 4);
-    SPK_W4_CASE(4, 1, 8);
-    SPK_W4_CASE(4, 2, 4);
-    SPK_W4_CASE(8, 1, 8);
+    if (tune.cg > 0) cg = tune.cg;
+    if (mt >= 4) ns = 1, cg = std::min(cg, 2);
+    while (cg > 1 && p.G % cg != 0) cg >>= 1;  // a chunk must not straddle a strip
+    int st = tune.st > 0 ? tune.st : (cg == 4 ? 2 : cg == 2 ? 4 : 8);
+    const bool dual = !whole && mt * ns <= 2;  // variant 3 keeps one accumulation chain for every M
+    const int cap = tune.ctas_per_sm, min_chunks = tune.min_units > 0 ? tune.min_units : 1;
+#define SPK_W4_CASE(MT_, NS_, CG_, ST_)                                                                  \
+    if (mt == MT_ && ns == NS_ && cg == CG_ && st == ST_) {                                              \
+        if (dual) return launch_stream_t<MT_, NS_, CG_, ST_, ASYM, (MT_ * NS_ <= 2)>(p, whole, cap, min_chunks, dev, stream); \
+        return launch_stream_t<MT_, NS_, CG_, ST_, ASYM, false>(p, whole, cap, min_chunks, dev, stream);  \
+    }
+    SPK_W4_CASE(1, 1, 1, 8)
+    SPK_W4_CASE(1, 1, 2, 4)
+    SPK_W4_CASE(1, 1, 4, 2)
+    SPK_W4_CASE(1, 2, 2, 2)
+    SPK_W4_CASE(2, 1, 1, 8)
+    SPK_W4_CASE(2, 1, 2, 4)
+    SPK_W4_CASE(2, 1, 4, 2)
+    SPK_W4_CASE(2, 2, 2, 2)
+    SPK_W4_CASE(4, 1, 1, 8)
+    SPK_W4_CASE(4, 1, 2, 4)
+    SPK_W4_CASE(8, 1, 1, 8)
+    SPK_W4_CASE(8, 1, 2, 4)
 #undef SPK_W4_CASE
-    return fail(SPK_INVALID, "w4gemm: no stream kernel for mt=%d ns=%d", mt, ns);
+    return fail(SPK_INVALID, "w4gemm: no stream kernel for mt=%d ns=%d cg=%d st=%d", mt, ns, cg, st);
 }
 
 }  // namespace
