@@ -683,3 +683,117 @@ extern "C" int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void*
     const bool whole = variant == 3;
     return zeros ? launch_stream<true>(p, whole, *dev, stream) : launch_stream<false>(p, whole, *dev, stream);
 }
+
+// ---- w4gemm without any allocation ---------------------------------------------------------------
+//
+// Some callers must not allocate device memory at all: a serving engine that has handed the whole
+// HBM budget to its own pool (a cudaMalloc there fails or eats into the pool's headroom), a process
+// that runs under a hard device-memory cap, and latency-critical loops that cannot afford the
+// device-wide synchronisation cudaMalloc implies.
+// spk_w4gemm_bf16 allocates its split-K scratch lazily through the per-device arena; this entry
+// point runs the same stream kernel (variant 2) with the scratch in a fixed array that is part of
+// the library image instead, so nothing is ever allocated or freed, here or in any routine it calls.
+//
+// The array is file-scope device memory: every GPU that loads the library holds its
+// kNoAllocBytes (8 MiB + 8 KiB + 256 B) until the process exits. That size fixes the limits of this
+// entry point: M <= 64, N <= 32768 (so M * N <= 2 Mi fp32 partials and N / 16 <= 2048 strip
+// counters). Larger problems are refused with SPK_INVALID; use spk_w4gemm_bf16 for them.
+//
+// All calls on a device share the one array. A call clears the part it is going to use before its
+// kernel runs (a memset on the same stream), because the array keeps whatever the previous call
+// left; two calls that overlap on the GPU (different streams, no dependency) race on it and must
+// be ordered by the caller.
+namespace spk {
+namespace {
+
+constexpr int kNoAllocMaxM = 64;
+constexpr int kNoAllocMaxN = 32768;
+constexpr size_t kNoAllocPartialBytes = static_cast<size_t>(kNoAllocMaxM) * kNoAllocMaxN * sizeof(float);
+constexpr size_t kNoAllocCounterBytes = (kNoAllocMaxN / 16) * sizeof(unsigned);
+constexpr size_t kNoAllocStatusBytes = 256;
+constexpr size_t kNoAllocBytes = kNoAllocPartialBytes + kNoAllocCounterBytes + kNoAllocStatusBytes;
+
+// In host code this name is only a handle for the runtime, not a device address: the address is
+// looked up once per device with cudaGetSymbolAddress and that pointer is what kernels receive.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+struct NoAllocDevice {
+    unsigned char* base = nullptr;  // device address of g_noalloc_scratch on this device
+    int sm_count = 0;
+};
+NoAllocDevice g_noalloc[16];
+
+// Set-up of the current device (first call on it): resolve the array's device address and read the
+// SM count. No allocation; cudaGetSymbolAddress may initialise the context and load the module,
+// which is why the first call on a device should happen before any stream capture.
+int noalloc_device(int* dev_out, NoAllocDevice** out) {
+    int dev = 0;
+    SPK_CUDA(cudaGetDevice(&dev));
+    SPK_REQUIRE(dev >= 0 && dev < 16, "w4gemm_noalloc: device ordinal %d not supported (max 16)", dev);
+    NoAllocDevice& d = g_noalloc[dev];
+    if (d.base == nullptr) {
+        int major = 0, sms = 0;
+        SPK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return fail(SPK_UNSUPPORTED, "this library is built for sm_100a only (device %d is sm_%dx)", dev, major);
+        SPK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        void* ptr = nullptr;
+        SPK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        SPK_REQUIRE(ptr != nullptr, "w4gemm_noalloc: the scratch array has no device address");
+        d.sm_count = sms;
+        d.base = static_cast<unsigned char*>(ptr);
+    }
+    *dev_out = dev;
+    *out = &d;
+    return SPK_OK;
+}
+
+}  // namespace
+}  // namespace spk
+
+extern "C" int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, const void* scales,
+                                       const uint8_t* zeros, void* C, int M, int N, int K, void* stream_) {
+    using namespace spk;
+    SPK_REQUIRE(M >= 1 && N > 0 && K > 0, "w4gemm_noalloc: M, N, K must be positive, got %d %d %d", M, N, K);
+    SPK_REQUIRE(N % 16 == 0 && K % w4::kGroup == 0,
+                "w4gemm_noalloc: needs N %% 16 == 0 and K %% 128 == 0, got N=%d K=%d", N, K);
+    SPK_REQUIRE(M <= kNoAllocMaxM && N <= kNoAllocMaxN,
+                "w4gemm_noalloc: M=%d N=%d exceed the fixed scratch of this entry point (M <= %d, N <= %d); "
+                "use spk_w4gemm_bf16 for larger problems",
+                M, N, kNoAllocMaxM, kNoAllocMaxN);
+    SPK_REQUIRE(A && packed && scales && C, "w4gemm_noalloc: null pointer");
+    SPK_REQUIRE(aligned16(A) && aligned16(packed) && aligned16(scales) && (!zeros || aligned16(zeros)),
+                "w4gemm_noalloc: A, packed, scales and zeros must be 16-byte aligned");
+    auto stream = static_cast<cudaStream_t>(stream_);
+    int dev = 0;
+    NoAllocDevice* nd = nullptr;
+    if (int rc = noalloc_device(&dev, &nd)) return rc;
+
+    // A local description of the device for the launcher: the fixed array instead of the arena.
+    DeviceState state;
+    state.device = dev;
+    state.sm_count = nd->sm_count;
+    state.partials = reinterpret_cast<float*>(nd->base);
+    state.counters = reinterpret_cast<unsigned*>(nd->base + kNoAllocPartialBytes);
+    state.status = reinterpret_cast<int*>(nd->base + kNoAllocPartialBytes + kNoAllocCounterBytes);
+    state.ready = true;
+
+    // The array keeps the last call's contents: clear what this call will accumulate into.
+    SPK_CUDA(cudaMemsetAsync(state.partials, 0, static_cast<size_t>(M) * N * sizeof(float), stream));
+    SPK_CUDA(cudaMemsetAsync(state.counters, 0, kNoAllocCounterBytes + kNoAllocStatusBytes, stream));
+
+    StreamParams p{};
+    p.A = static_cast<const __nv_bfloat16*>(A);
+    p.packed = reinterpret_cast<const unsigned char*>(packed);
+    p.scales = static_cast<const unsigned char*>(scales);
+    p.zeros = zeros;
+    p.C = static_cast<__nv_bfloat16*>(C);
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.G = K / w4::kGroup;
+    p.T = N / 16;
+    p.partials = state.partials;
+    p.counters = state.counters;
+    p.status = state.status;
+    return zeros ? launch_stream<true>(p, false, state, stream) : launch_stream<false>(p, false, state, stream);
+}

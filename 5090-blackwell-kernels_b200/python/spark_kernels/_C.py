@@ -47,6 +47,7 @@ _spk_device_status = _sig("spk_device_status", [_p, ctypes.POINTER(_i)])
 _spk_w4_quantize = _sig("spk_w4_quantize_bf16", [_p, _p, _p, _p, _i, _i, _p])
 _spk_w4_repack = _sig("spk_w4_repack", [_p, _p, _i, _i, _p])
 _spk_w4gemm = _sig("spk_w4gemm_bf16", [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
+_spk_w4gemm_noalloc = _sig("spk_w4gemm_bf16_noalloc", [_p, _p, _p, _p, _p, _i, _i, _i, _p])
 _sig("spk_w4gemm_num_variants", [])
 _sig("spk_w4gemm_default_variant", [])
 _sig("spk_w4gemm_supports", [_i, _i, _i, _i])
@@ -195,4 +196,30 @@ def w4gemm(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, zeros=No
             variant, _lib.spk_w4gemm_num_variants())
         _status(_spk_w4gemm(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros), out.data_ptr(),
                             M, N, K, v, _stream(a)))
+    return out
+
+
+def w4gemm_noalloc(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, zeros, out: torch.Tensor) -> torch.Tensor:
+    """w4gemm for callers that must not allocate device memory (no counterpart in the reference):
+    the caller passes `out` [M, N] bf16, and the library's split-K scratch is a fixed array inside
+    the library image instead of lazily allocated memory. Limits: M <= 64, N <= 32768 (ValueError
+    beyond). Calls on one device share that array, so calls that could overlap on the GPU must be
+    ordered by the caller; make the first call on a device before any stream capture."""
+    for t, name in ((a, "a"), (packed, "packed"), (scales, "scales"), (out, "out")):
+        _check_cuda_contig(t, name)
+    _check(a.dtype == torch.bfloat16 and a.dim() == 2, "w4gemm_noalloc expects a 2-D bfloat16 a")
+    _check(packed.dtype == torch.int32 and packed.dim() == 2, "packed must be the int32 [N/16, 2K] tensor from w4_repack")
+    M, K = a.shape
+    N = packed.shape[0] * 16
+    _check(packed.shape[1] == 2 * K, f"packed is {list(packed.shape)}, expected [N/16, {2 * K}]")
+    _check(scales.dtype == torch.bfloat16 and tuple(scales.shape) == (K // W4_GROUP, N),
+           f"scales must be bfloat16 [{K // W4_GROUP}, {N}]")
+    if zeros is not None:
+        _check_cuda_contig(zeros, "zeros")
+        _check(zeros.dtype == torch.uint8 and tuple(zeros.shape) == (K // W4_GROUP, N), "zeros must be uint8 [K/128, N]")
+    _check(out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N) and out.device == a.device,
+           "out must be bfloat16 [M, N] on a's device")
+    with torch.cuda.device(a.device):
+        _status(_spk_w4gemm_noalloc(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros),
+                                    out.data_ptr(), M, N, K, _stream(a)))
     return out

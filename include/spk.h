@@ -60,6 +60,17 @@ SPK_API int spk_w4_repack(const int32_t* qweight, int32_t* packed, int K, int N,
 SPK_API int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void* scales,
                             const uint8_t* zeros, void* C, int M, int N, int K, int variant,
                             void* stream);
+/* No counterpart in the reference. The same GEMM as spk_w4gemm_bf16 variant 2 for callers that
+ * must not allocate device memory (a serving engine whose pool owns all of HBM, a process
+ * under a hard device-memory cap, latency-critical loops that cannot take cudaMalloc's
+ * device-wide synchronisation): the split-K scratch is a fixed array inside the library image (about 8 MiB,
+ * held by every GPU that loads the library until the process exits), nothing is allocated or
+ * freed. Limits from that array: M <= 64 and N <= 32768, larger sizes return SPK_INVALID. The
+ * first call on a device resolves the array's address (make it before any stream capture). All
+ * calls on a device share the array; a call clears the part it uses first, and calls that overlap
+ * on the GPU race on it, so order them. */
+SPK_API int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, const void* scales,
+                                    const uint8_t* zeros, void* C, int M, int N, int K, void* stream);
 /* reference include/spark/kernels.h:414-416 */
 SPK_API int spk_w4gemm_num_variants(void);
 SPK_API int spk_w4gemm_default_variant(void);
