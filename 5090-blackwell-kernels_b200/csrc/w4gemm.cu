@@ -198,7 +198,7 @@ struct Slot {
 // (measured: 25% L1 misses doubled the kernel time).
 template <int MT>
 struct ActRing {
-    static constexpr int kStages = MT <= 2 ? 8 : (MT == 4 ? 4 : 2);  // 8 MT rows x (CG x 256 + 64) bytes per stage
+    static constexpr int kStages = MT == 1 ? 8 : (MT == 2 ? 4 : (MT == 4 ? 3 : 2));  // 8 MT rows x (CG x 256 + 64) bytes per stage
 };
 // Row pitch: chunk bytes + 64, so that the eight lanes of a quarter warp (two token rows x four
 // 16-byte columns) fall into distinct 16-byte bank groups.
@@ -284,7 +284,7 @@ w4_stream_kernel(const StreamParams p) {
     // copy per token row issued by lane r. It runs kActLead chunks ahead of warp 0's own
     // consumption, which leaves the other warps kActStages - kActLead chunks of slack before
     // warp 0 would have to wait for them.
-    constexpr int kActLead = kActStages > 4 ? kActStages - 3 : kActStages - 1;
+    constexpr int kActLead = kActStages > 4 ? kActStages - 3 : (kActStages > 2 ? kActStages - 1 : kActStages);
     const unsigned char* a_row = reinterpret_cast<const unsigned char*>(p.A) +
                                  static_cast<size_t>(tok0 + (lane < rows ? lane : 0)) * p.K * 2;
     int a_issued = 0, a_ch = ch0, a_pstage = 0;
@@ -595,7 +595,7 @@ template <bool ASYM>
 int launch_stream(const StreamParams& p, bool whole, const DeviceState& dev, cudaStream_t stream) {
     static const StreamTuning tune = read_tuning();
     int mt = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
-    int ns = 1, cg = mt <= 2 ? 4 : 2;
+    int ns = 1, cg = mt == 1 ? 4 : 2;
     if (tune.mt > 0 && (p.M <= 8 * tune.mt || tune.mt == 8)) mt = tune.mt;
     if (tune.ns > 0) ns = tune.ns;
     if (tune.cg > 0) cg = tune.cg;

@@ -223,3 +223,243 @@ def w4gemm_noalloc(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
         _status(_spk_w4gemm_noalloc(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros),
                                     out.data_ptr(), M, N, K, _stream(a)))
     return out
+
+
+# ---- fp8 --------------------------------------------------------------------------------------
+
+_u8p = _p
+_spk_fp8_quantize = _sig("spk_fp8_quantize", [_p, _p, _p, _p, _i, _i, _i, _p])
+_spk_fp8gemm = _sig("spk_fp8gemm", [_p, _p, _p, _i, _i, _i, _p, _p, _i, _p])
+_spk_fp8gemm_mx = _sig("spk_fp8gemm_mx", [_p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p])
+_spk_fp8gemm_block128 = _sig("spk_fp8gemm_block128", [_p, _p, _p, _i, _i, _i, _p, _p, _p])
+_spk_fp8_quantize_block128 = _sig("spk_fp8_quantize_block128", [_p, _p, _p, _i, _i, _i, _p])
+_sig("spk_fp8gemm_num_variants", [])
+_sig("spk_fp8gemm_default_variant", [])
+_sig("spk_fp8gemm_supports", [_i, _i, _i, _i])
+_sig("spk_fp8gemm_mx_supports", [_i, _i, _i, _i])
+_sig("spk_fp8gemm_v3_set_route", [_i], None)
+_sig("spk_fp8gemm_v3_route", [])
+_sig("spk_fp8gemm_v3_num_tiles", [])
+_sig("spk_fp8gemm_v3_route_name", [_i, _i, _i, _i], ctypes.c_char_p)
+_sig("spk_fp8gemm_v4_route_name", [_i, _i, _i], ctypes.c_char_p)
+_spk_fp4_scale_bytes = _sig("spk_fp4_scale_bytes", [_i, _i, _i], ctypes.c_size_t)
+_spk_fp4_quantize = _sig("spk_fp4_quantize", [_p, _p, _p, _i, _i, _p, _i, _p, _p, _p])
+_spk_fp4gemm = _sig("spk_fp4gemm", [_p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p])
+_sig("spk_fp4gemm_num_variants", [])
+_sig("spk_fp4gemm_supports", [_i, _i, _i, _i])
+
+_FP8 = torch.float8_e4m3fn
+
+
+def _scalar_ptrs(scale_a, scale_b, like, op):
+    if scale_a is None:
+        return None, None
+    for sc in (scale_a, scale_b):
+        _check(sc.is_cuda and sc.dtype == torch.float32 and sc.numel() == 1,
+               "scale_a and scale_b must be float32 CUDA tensors with one element")
+        _check(sc.device == like.device, "scales must be on a's device")
+    return scale_a.data_ptr(), scale_b.data_ptr()
+
+
+def fp8gemm(a, b_t, scale_a=None, scale_b=None, variant: int = -1, sfa=None, sfb=None):
+    """(scale_a * scale_b) * (a @ b_t.T) -> bf16 [M, N]; a [M, K], b_t [N, K] float8_e4m3fn. With
+    sfa [M, K/32] / sfb [N, K/32] uint8: MX mode (reference python/csrc/bindings.cpp:333-400)."""
+    _check_cuda_contig(a, "a")
+    _check_cuda_contig(b_t, "b_t")
+    _check(a.dtype == _FP8 and b_t.dtype == _FP8, "fp8gemm expects float8_e4m3fn inputs")
+    _check(a.dim() == 2 and b_t.dim() == 2, "fp8gemm expects 2-D tensors")
+    _check(a.shape[1] == b_t.shape[1],
+           f"inner dimensions mismatch: a is {a.shape[0]}x{a.shape[1]}, b_t is {b_t.shape[0]}x{b_t.shape[1]} (b_t is [N, K])")
+    mx = sfa is not None or sfb is not None
+    _check(not mx or (sfa is not None and sfb is not None),
+           "fp8gemm: sfa and sfb must both be given (MX mode) or both be None")
+    _check(mx or (scale_a is not None and scale_b is not None),
+           "fp8gemm: scale_a and scale_b are required without block scales")
+    _check((scale_a is None) == (scale_b is None), "fp8gemm: scale_a and scale_b must both be given or both be None")
+    sa, sb = _scalar_ptrs(scale_a, scale_b, a, "fp8gemm")
+    _check(_aligned16(a) and _aligned16(b_t), "fp8gemm needs 16-byte aligned a and b_t storage")
+    M, K = a.shape
+    N = b_t.shape[0]
+    if mx:
+        _check(K % 256 == 0, f"fp8gemm with block scales needs K a multiple of 256, got {K}")
+        for sf, name, rows in ((sfa, "sfa", M), (sfb, "sfb", N)):
+            _check_cuda_contig(sf, name)
+            _check(sf.dtype == torch.uint8, f"{name} must be uint8 (ue8m0: exponent + 127)")
+            _check(sf.dim() == 2 and tuple(sf.shape) == (rows, K // 32), f"{name} must be [{rows}, {K // 32}], got {list(sf.shape)}")
+            _check(sf.device == a.device, f"{name} must be on a's device")
+            _check(_aligned16(sf), f"{name} needs 16-byte aligned storage")
+    with torch.cuda.device(a.device):
+        c = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        sup = _lib.spk_fp8gemm_mx_supports if mx else _lib.spk_fp8gemm_supports
+        v = _lib.spk_fp8gemm_default_variant() if variant < 0 else _resolve_variant(variant, _lib.spk_fp8gemm_num_variants())
+        while variant < 0 and v > 0 and not sup(M, N, K, v):
+            v -= 1
+        if mx:
+            _status(_spk_fp8gemm_mx(a.data_ptr(), b_t.data_ptr(), c.data_ptr(), M, N, K, sa, sb, sfa.data_ptr(),
+                                    sfb.data_ptr(), v, _stream(a)))
+        else:
+            _status(_spk_fp8gemm(a.data_ptr(), b_t.data_ptr(), c.data_ptr(), M, N, K, sa, sb, v, _stream(a)))
+    return c
+
+
+def fp8gemm_v3_set_route(route: int) -> int:
+    prev = _lib.spk_fp8gemm_v3_route()
+    n = _lib.spk_fp8gemm_v3_num_tiles()
+    _check(-2 <= route < n, f"fp8gemm_v3_set_route: {route} is not -1, -2 or a tile in [0, {n})")
+    _lib.spk_fp8gemm_v3_set_route(route)
+    return prev
+
+
+def fp8gemm_v3_route_name(M: int, N: int, K: int, mx: bool = False) -> str:
+    return _lib.spk_fp8gemm_v3_route_name(M, N, K, int(mx)).decode()
+
+
+def fp8gemm_v3_num_tiles() -> int:
+    return _lib.spk_fp8gemm_v3_num_tiles()
+
+
+def fp8gemm_v4_route_name(M: int, N: int, K: int) -> str:
+    return _lib.spk_fp8gemm_v4_route_name(M, N, K).decode()
+
+
+def fp8_quantize(x: torch.Tensor, mode: str = "tensor"):
+    """bf16 [rows, K] -> (e4m3 [rows, K], scales): f32 [1] ("tensor"), f32 [rows, 1] ("row") or
+    uint8 [rows, K/32] ("mx") (reference python/csrc/bindings.cpp:489-527)."""
+    _check_cuda_contig(x, "x")
+    _check(x.dtype == torch.bfloat16, "fp8_quantize expects bfloat16 x")
+    _check(x.dim() == 2, "fp8_quantize expects a 2-D [rows, K] tensor")
+    _check(_aligned16(x), "fp8_quantize needs 16-byte aligned x storage")
+    rows, K = x.shape
+    _check(mode in ("tensor", "row", "mx"), f"fp8_quantize mode must be 'tensor', 'row' or 'mx', got {mode}")
+    m = {"tensor": 0, "row": 1, "mx": 2}[mode]
+    _check(K % (32 if m == 2 else 8) == 0, f"fp8_quantize needs K a multiple of 8 (32 for mx), got {K}")
+    _check(rows > 0 and K > 0, "fp8_quantize needs a non-empty x")
+    with torch.cuda.device(x.device):
+        q = torch.empty((rows, K), dtype=_FP8, device=x.device)
+        work = None
+        if m == 0:
+            work = torch.zeros(2, dtype=torch.float32, device=x.device)  # [amax bits, scale]
+            scale = work[1:2]
+        elif m == 1:
+            scale = torch.empty((rows, 1), dtype=torch.float32, device=x.device)
+        else:
+            scale = torch.empty((rows, K // 32), dtype=torch.uint8, device=x.device)
+        _status(_spk_fp8_quantize(x.data_ptr(), q.data_ptr(), scale.data_ptr(), _ptr(work), rows, K, m, _stream(x)))
+    return q, scale
+
+
+def fp8_quantize_block128(x: torch.Tensor, block_rows: int):
+    """float32 [rows, K] -> (e4m3 [rows, K], f32 scales [cdiv(rows, block_rows), K/128]); an
+    addition to the reference's surface (fp32 block scales: 1 for activations, 128 for weights)."""
+    _check_cuda_contig(x, "x")
+    _check(x.dtype == torch.float32 and x.dim() == 2, "fp8_quantize_block128 expects a 2-D float32 x")
+    rows, K = x.shape
+    with torch.cuda.device(x.device):
+        q = torch.empty((rows, K), dtype=_FP8, device=x.device)
+        s = torch.empty(((rows + block_rows - 1) // block_rows, K // 128), dtype=torch.float32, device=x.device)
+        _status(_spk_fp8_quantize_block128(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, K, block_rows, _stream(x)))
+    return q, s
+
+
+def fp8gemm_block128(a, b_t, scale_a_blocks, scale_b_blocks):
+    """fp8 GEMM with fp32 block scales (a: 1x128 blocks [M, K/128], b_t: 128x128 blocks
+    [cdiv(N,128), K/128]) -> bf16 [M, N]; an addition to the reference's surface."""
+    for t, name in ((a, "a"), (b_t, "b_t"), (scale_a_blocks, "scale_a_blocks"), (scale_b_blocks, "scale_b_blocks")):
+        _check_cuda_contig(t, name)
+    _check(a.dtype == _FP8 and b_t.dtype == _FP8 and a.dim() == 2 and b_t.dim() == 2, "fp8gemm_block128 expects 2-D float8_e4m3fn a, b_t")
+    M, K = a.shape
+    N = b_t.shape[0]
+    _check(b_t.shape[1] == K, "inner dimensions mismatch")
+    _check(K % 128 == 0, f"fp8gemm_block128 needs K a multiple of 128, got {K}")
+    _check(scale_a_blocks.dtype == torch.float32 and tuple(scale_a_blocks.shape) == (M, K // 128), "scale_a_blocks must be f32 [M, K/128]")
+    _check(scale_b_blocks.dtype == torch.float32 and tuple(scale_b_blocks.shape) == ((N + 127) // 128, K // 128),
+           "scale_b_blocks must be f32 [cdiv(N,128), K/128]")
+    with torch.cuda.device(a.device):
+        c = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        _status(_spk_fp8gemm_block128(a.data_ptr(), b_t.data_ptr(), c.data_ptr(), M, N, K, scale_a_blocks.data_ptr(),
+                                      scale_b_blocks.data_ptr(), _stream(a)))
+    return c
+
+
+# ---- fp4 --------------------------------------------------------------------------------------
+
+def _fp4_format(fmt: str) -> int:
+    _check(fmt in ("nvfp4", "mxfp4"), f"fp4 format must be 'nvfp4' or 'mxfp4', got '{fmt}'")
+    return 0 if fmt == "nvfp4" else 1
+
+
+_FP4X2 = getattr(torch, "float4_e2m1fn_x2", None)
+_E8M0 = getattr(torch, "float8_e8m0fnu", None)
+
+
+def fp4_scale_bytes(rows: int, K: int, fmt: str = "nvfp4") -> int:
+    return int(_spk_fp4_scale_bytes(rows, K, _fp4_format(fmt)))
+
+
+def _check_fp4_bytes(t, name):
+    _check_cuda_contig(t, name)
+    _check(t.dtype == torch.uint8 or (_FP4X2 is not None and t.dtype == _FP4X2),
+           f"{name} must be uint8 or float4_e2m1fn_x2 (packed e2m1), got {t.dtype}")
+    _check(t.dim() == 2, f"{name} must be 2-D [rows, K / 2]")
+    _check(_aligned16(t), f"{name} needs 16-byte aligned storage")
+
+
+def _check_fp4_scales(t, name, rows, K, format, like):
+    _check_cuda_contig(t, name)
+    ok = t.dtype == torch.uint8 or (format == 0 and t.dtype == _FP8) or (format == 1 and _E8M0 is not None and t.dtype == _E8M0)
+    _check(ok, f"{name} must be uint8 or the format's float8 scale type, got {t.dtype}")
+    want = int(_spk_fp4_scale_bytes(rows, K, format))
+    _check(t.numel() == want, f"{name} must hold the blocked scale layout of {rows} rows ({want} bytes, rows padded to 128), got {t.numel()}")
+    _check(t.device == like.device, f"{name} must be on a's device")
+    _check(_aligned16(t), f"{name} needs 16-byte aligned storage")
+
+
+def fp4_quantize(x: torch.Tensor, fmt: str = "nvfp4", scale=None):
+    """(q uint8 [rows, K/2], sf uint8 flat blocked, scale 0-dim f32 | None)
+    (reference python/csrc/bindings.cpp:446-487)."""
+    _check_cuda_contig(x, "x")
+    _check(x.dtype == torch.bfloat16, "fp4_quantize expects bfloat16 x")
+    _check(x.dim() == 2, "fp4_quantize expects a 2-D [rows, K] tensor")
+    _check(_aligned16(x), "fp4_quantize needs 16-byte aligned x storage")
+    format = _fp4_format(fmt)
+    rows, K = x.shape
+    _check(K % (128 if format == 1 else 64) == 0, f"fp4_quantize needs K a multiple of 64 (nvfp4) or 128 (mxfp4), got {K}")
+    with torch.cuda.device(x.device):
+        s, work = None, None
+        if format == 0:
+            if scale is not None:
+                _check(scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == 1 and scale.device == x.device,
+                       "scale must be a float32 CUDA tensor with one element on x's device")
+                s = scale.reshape(()).contiguous()
+            else:
+                work = torch.zeros(2, dtype=torch.float32, device=x.device)  # [amax bits, scale]
+                s = work[1].reshape(())
+        q = torch.empty((rows, K // 2), dtype=torch.uint8, device=x.device)
+        sf = torch.empty((int(_spk_fp4_scale_bytes(rows, K, format)),), dtype=torch.uint8, device=x.device)
+        _status(_spk_fp4_quantize(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, K, _ptr(s), format, _stream(x),
+                                  _ptr(work), _ptr(s) if work is not None else None))
+    return q, sf, s
+
+
+def fp4gemm(a, b_t, sfa, sfb, scale_a=None, scale_b=None, fmt: str = "nvfp4", variant: int = -1):
+    """scale_a * scale_b * (A @ B_t.T) for packed e2m1 a [M, K/2], b_t [N, K/2] with blocked block
+    scales -> bf16 [M, N] (reference python/csrc/bindings.cpp:529-568)."""
+    _check_fp4_bytes(a, "a")
+    _check_fp4_bytes(b_t, "b_t")
+    format = _fp4_format(fmt)
+    _check(a.shape[1] == b_t.shape[1],
+           f"inner dimensions mismatch: a is {a.shape[0]}x{a.shape[1]} bytes, b_t is {b_t.shape[0]}x{b_t.shape[1]} (both [rows, K / 2])")
+    _check(b_t.device == a.device, "b_t must be on a's device")
+    M, N, K = a.shape[0], b_t.shape[0], 2 * a.shape[1]
+    _check((scale_a is None) == (scale_b is None), "fp4gemm: scale_a and scale_b must both be given or both be None")
+    sa, sb = _scalar_ptrs(scale_a, scale_b, a, "fp4gemm")
+    _check_fp4_scales(sfa, "sfa", M, K, format, a)
+    _check_fp4_scales(sfb, "sfb", N, K, format, a)
+    with torch.cuda.device(a.device):
+        c = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        v = _resolve_variant(variant, _lib.spk_fp4gemm_num_variants())
+        while variant < 0 and v > 0 and not _lib.spk_fp4gemm_supports(M, N, K, v):
+            v -= 1
+        _status(_spk_fp4gemm(a.data_ptr(), b_t.data_ptr(), c.data_ptr(), M, N, K, sfa.data_ptr(), sfb.data_ptr(), sa, sb,
+                             format, v, _stream(a)))
+    return c

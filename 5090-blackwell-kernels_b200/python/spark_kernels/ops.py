@@ -68,3 +68,40 @@ def w4gemm(a: torch.Tensor, w, scales: torch.Tensor | None = None, zeros: torch.
 
 def num_variants(name: str) -> int:
     return _C.num_variants(name)
+
+
+def fp8gemm(a, b_t, scale_a=None, scale_b=None, variant: int = -1, sfa=None, sfb=None):
+    """fp8 GEMM: (scale_a * scale_b) * (a @ b_t.T) -> [M, N] bf16, fp32 accumulate. a [M, K] and
+    b_t [N, K] are float8_e4m3fn, K-contiguous (b_t as nn.Linear stores a weight). scale_a / scale_b
+    are one-element float32 CUDA tensors. With `sfa` [M, K/32] and `sfb` [N, K/32] (uint8 E8M0,
+    exponent + 127) every product is also scaled by its two block scales (MXFP8; K % 256 == 0) and
+    the per-tensor scales may be omitted. N and K multiples of 64, any M >= 1 (variant 1, 3, 4)."""
+    return _C.fp8gemm(a, b_t, scale_a, scale_b, variant, sfa, sfb)
+
+
+def fp8_quantize(x, mode: str = "tensor"):
+    """bf16 [rows, K] -> (e4m3, scale): "tensor" one power-of-two fp32 scale [1], "row" one per row
+    [rows, 1], "mx" a uint8 E8M0 byte per 32 values [rows, K/32] (the OCP recipe). Elements are
+    x / scale rounded to nearest even, saturating at 448."""
+    return _C.fp8_quantize(x, mode)
+
+
+def fp4_quantize(x, fmt: str = "nvfp4", scale=None):
+    """bf16 [rows, K] -> (q uint8 [rows, K/2], sf blocked uint8, scale). nvfp4: e4m3 scale per 16 on
+    a per-tensor fp32 decode scale (`scale`, or max|x| / (6 * 448) computed on the device);
+    mxfp4: E8M0 scale per 32, scale None."""
+    return _C.fp4_quantize(x, fmt, scale)
+
+
+def fp4gemm(a, b_t, sfa, sfb, scale_a=None, scale_b=None, fmt: str = "nvfp4", variant: int = -1):
+    """fp4 block-scaled GEMM: scale_a * scale_b * (A @ B_t.T) -> [M, N] bf16. a [M, K/2], b_t [N, K/2]
+    packed e2m1, sfa / sfb blocked block scales. N % 64 == 0, K % 256 == 0, any M (variant 1)."""
+    return _C.fp4gemm(a, b_t, sfa, sfb, scale_a, scale_b, fmt, variant)
+
+
+def fp8_quantize_block128(x, block_rows: int):
+    return _C.fp8_quantize_block128(x, block_rows)
+
+
+def fp8gemm_block128(a, b_t, scale_a_blocks, scale_b_blocks):
+    return _C.fp8gemm_block128(a, b_t, scale_a_blocks, scale_b_blocks)

@@ -76,6 +76,69 @@ SPK_API int spk_w4gemm_num_variants(void);
 SPK_API int spk_w4gemm_default_variant(void);
 SPK_API int spk_w4gemm_supports(int M, int N, int K, int variant);
 
+/* ---- fp8 e4m3 ------------------------------------------------------------------------------ */
+
+enum { SPK_FP8Q_TENSOR = 0, SPK_FP8Q_ROW = 1, SPK_FP8Q_MX = 2 };  /* reference kernels.h:359 */
+
+/* reference include/spark/kernels.h:362 (absmax_bits): atomicMax of max|x| over n bf16 values into
+ * *work as float bits; *work must hold zero or a smaller amax. n % 8 == 0, x 16-byte aligned. */
+SPK_API int spk_absmax_bits(const void* x, long long n, unsigned* work, void* stream);
+/* reference include/spark/kernels.h:363-364 (fp8_quantize): x bf16 [rows][K] -> q e4m3 [rows][K]
+ * plus scales: TENSOR float[1] (work: one zeroed unsigned), ROW float[rows], MX u8 [rows][K/32]. */
+SPK_API int spk_fp8_quantize(const void* x, unsigned char* q, void* scale, unsigned* work, int rows,
+                             int K, int mode, void* stream);
+/* reference include/spark/kernels.h:260-261 (fp8gemm): C bf16 [M][N] = sa sb A Bt^T, A [M][K] and
+ * Bt [N][K] e4m3, scale_a / scale_b device fp32 scalars. N % 64 == 0, K % 64 == 0. */
+SPK_API int spk_fp8gemm(const void* A, const void* Bt, void* C, int M, int N, int K,
+                        const float* scale_a, const float* scale_b, int variant, void* stream);
+/* reference include/spark/kernels.h:273-275 (fp8gemm_mx): ue8m0 scales sfa [M][K/32], sfb [N][K/32]
+ * row-major; scale_a / scale_b may both be NULL. K % 256 == 0. */
+SPK_API int spk_fp8gemm_mx(const void* A, const void* Bt, void* C, int M, int N, int K,
+                           const float* scale_a, const float* scale_b, const unsigned char* sfa,
+                           const unsigned char* sfb, int variant, void* stream);
+/* reference include/spark/kernels.h:262-265,276,280 */
+SPK_API int spk_fp8gemm_num_variants(void);
+SPK_API int spk_fp8gemm_default_variant(void);
+SPK_API int spk_fp8gemm_supports(int M, int N, int K, int variant);
+SPK_API int spk_fp8gemm_mx_supports(int M, int N, int K, int variant);
+SPK_API int spk_fp8gemm_mx_available(void);
+/* reference include/spark/kernels.h:287-294 (variant 3's route; -1 the rule, -2 CUDA cores only) */
+SPK_API void spk_fp8gemm_v3_set_route(int route);
+SPK_API int spk_fp8gemm_v3_route(void);
+SPK_API int spk_fp8gemm_v3_num_tiles(void);
+SPK_API const char* spk_fp8gemm_v3_route_name(int M, int N, int K, int mx);
+SPK_API const char* spk_fp8gemm_v4_route_name(int M, int N, int K);
+/* No counterpart in the reference (its fp8 modes are per-tensor and MX): fp32 block scales, sA
+ * [M][K/128] (1 x 128 blocks of A) and sB [cdiv(N,128)][K/128] (128 x 128 blocks of Bt):
+ * C = bf16( sum_kb (sum_{k in kb} a b) sA[m][kb] sB[n/128][kb] ). K % 128 == 0, N % 64 == 0. */
+SPK_API int spk_fp8gemm_block128(const void* A, const void* Bt, void* C, int M, int N, int K,
+                                 const float* sA, const float* sB, void* stream);
+/* No counterpart in the reference: the quantizer of that mode. x fp32 [rows][K]; block_rows 1 or
+ * 128; s = amax / 448 per block (1 for an all-zero block), q = e4m3(x / s). */
+SPK_API int spk_fp8_quantize_block128(const float* x, unsigned char* q, float* scales, int rows, int K,
+                                      int block_rows, void* stream);
+
+/* ---- fp4 e2m1 (NVFP4, MXFP4) -------------------------------------------------------------- */
+
+enum { SPK_FP4_NVFP4 = 0, SPK_FP4_MXFP4 = 1 };  /* reference kernels.h:322 */
+
+/* reference include/spark/kernels.h:331 (fp4_scale_bytes) */
+SPK_API size_t spk_fp4_scale_bytes(int rows, int K, int format);
+/* reference include/spark/kernels.h:345-347 (fp4_quantize): x bf16 [rows][K] -> q [rows][K/2] and sf
+ * (blocked layout, every byte written). NVFP4: `scale` the decode scale (NULL: 1), or with `work`
+ * (a zeroed unsigned) max|x| / (6 * 448) computed on the device and written to *scale_out. */
+SPK_API int spk_fp4_quantize(const void* x, unsigned char* q, unsigned char* sf, int rows, int K,
+                             const float* scale, int format, void* stream, unsigned* work,
+                             float* scale_out);
+/* reference include/spark/kernels.h:323-325 (fp4gemm). N % 64 == 0, K % 256 == 0. */
+SPK_API int spk_fp4gemm(const void* A, const void* Bt, void* C, int M, int N, int K,
+                        const unsigned char* sfa, const unsigned char* sfb, const float* scale_a,
+                        const float* scale_b, int format, int variant, void* stream);
+/* reference include/spark/kernels.h:326-329 */
+SPK_API int spk_fp4gemm_num_variants(void);
+SPK_API int spk_fp4gemm_supports(int M, int N, int K, int variant);
+SPK_API int spk_fp4gemm_available(void);
+
 #ifdef __cplusplus
 }
 #endif
