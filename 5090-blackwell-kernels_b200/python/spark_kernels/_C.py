@@ -463,3 +463,49 @@ def fp4gemm(a, b_t, sfa, sfb, scale_a=None, scale_b=None, fmt: str = "nvfp4", va
         _status(_spk_fp4gemm(a.data_ptr(), b_t.data_ptr(), c.data_ptr(), M, N, K, sfa.data_ptr(), sfb.data_ptr(), sa, sb,
                              format, v, _stream(a)))
     return c
+
+
+# ---- launch rules of the decode kernels (reference python/csrc/bindings.cpp:1797-1829) ----------
+
+_sig("spk_device_shape_sm_count", [])
+_sig("spk_device_shape_l2_bytes", [], _i64)
+_sig("spk_device_shape_spec_gbps", [], ctypes.c_double)
+_sig("spk_device_shape_bytes_in_flight", [], _i64)
+_sig("spk_device_shape_forced", [])
+_sig("spk_decode_split_k", [_i64, _i, _i, _i64, _i, _i])
+_sig("spk_decode_need_ctas", [_i64, _i])
+_sig("spk_decode_fits_l2", [_i64, _i])
+_sig("spk_decode_force_split_k", [_i], None)
+_sig("spk_decode_forced_split_k", [])
+
+
+def _decode_device(device: str) -> int:
+    table = {"": 0, "current": 0, "gb10": 1, "rtx5090": 2, "b200": 3}
+    if device not in table:
+        raise ValueError(f"device must be '', 'gb10', 'rtx5090' or 'b200', got '{device}'")
+    return table[device]
+
+
+def device_shape() -> dict:
+    return {"sm_count": _lib.spk_device_shape_sm_count(), "l2_bytes": _lib.spk_device_shape_l2_bytes(),
+            "spec_gbps": _lib.spk_device_shape_spec_gbps(), "bytes_in_flight": _lib.spk_device_shape_bytes_in_flight(),
+            "forced": bool(_lib.spk_device_shape_forced())}
+
+
+def split_k_for(weight_bytes: int, tiles: int, max_split: int, per_cta_in_flight: int, slots: int, device: str = "") -> int:
+    _check(tiles >= 1 and max_split >= 1 and per_cta_in_flight >= 1 and slots >= 0,
+           "split_k_for: tiles, max_split and per_cta_in_flight must be >= 1, slots >= 0")
+    return _lib.spk_decode_split_k(weight_bytes, tiles, max_split, per_cta_in_flight, slots, _decode_device(device))
+
+
+def need_ctas(per_cta_in_flight: int, device: str = "") -> int:
+    _check(per_cta_in_flight >= 1, "need_ctas: per_cta_in_flight must be >= 1")
+    return _lib.spk_decode_need_ctas(per_cta_in_flight, _decode_device(device))
+
+
+def fits_l2(nbytes: int, device: str = "") -> bool:
+    return bool(_lib.spk_decode_fits_l2(nbytes, _decode_device(device)))
+
+
+def decode_force_split_k(split: int) -> None:
+    _lib.spk_decode_force_split_k(split)

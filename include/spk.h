@@ -139,6 +139,26 @@ SPK_API int spk_fp4gemm_num_variants(void);
 SPK_API int spk_fp4gemm_supports(int M, int N, int K, int variant);
 SPK_API int spk_fp4gemm_available(void);
 
+/* ---- launch rules of the decode kernels ----------------------------------------------------- */
+
+/* reference include/spark/kernels.h:1044 (DecodeDevice) plus the B200 constants */
+enum { SPK_DEVICE_CURRENT = 0, SPK_DEVICE_GB10 = 1, SPK_DEVICE_RTX5090 = 2, SPK_DEVICE_B200 = 3 };
+
+/* reference include/spark/kernels.h:1033-1037 (device_shape_*) */
+SPK_API int spk_device_shape_sm_count(void);
+SPK_API int64_t spk_device_shape_l2_bytes(void);
+SPK_API double spk_device_shape_spec_gbps(void);
+SPK_API int64_t spk_device_shape_bytes_in_flight(void);
+SPK_API int spk_device_shape_forced(void);
+/* reference include/spark/kernels.h:1045-1052 (decode_*): host arithmetic, no CUDA call for a named
+ * device; -1 for an unknown device. */
+SPK_API int spk_decode_split_k(int64_t weight_bytes, int tiles, int max_split,
+                               int64_t per_cta_in_flight, int slots, int device);
+SPK_API int spk_decode_need_ctas(int64_t per_cta_in_flight, int device);
+SPK_API int spk_decode_fits_l2(int64_t bytes, int device);
+SPK_API void spk_decode_force_split_k(int split);
+SPK_API int spk_decode_forced_split_k(void);
+
 #ifdef __cplusplus
 }
 #endif
