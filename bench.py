@@ -266,11 +266,37 @@ def run_ours(args) -> None:
     ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
 
+    # BASELINE config 4: the full-depth projection stack (qkv, o, gate|up, down of 32 layers) at 64 tokens
+    del gu, dn
+    torch.cuda.empty_cache()
+    from spark_kernels import tp as tpmod
+
+    stack = tpmod.ProjectionStack(sk, tpmod.LlamaShape(), 64, rank, tp, dev, seed=99)
+    reduce_fn = (lambda t: dist.all_reduce(t)) if world > 1 else None
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        stack.run(reduce_fn)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    sgraph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(sgraph):
+        stack.run(reduce_fn)
+    for _ in range(3):
+        sgraph.replay()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        sgraph.replay()
+    s1.record()
+    barrier()
+    ms_stack = s0.elapsed_time(s1)
+
     status = sk._C.device_status()
     if world > 1:
-        t = torch.tensor([ms_total, ms_e2e, float(status)], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_total, ms_e2e, float(status), ms_stack], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e, status = t[0].item(), t[1].item(), int(t[2].item())
+        ms_total, ms_e2e, status, ms_stack = t[0].item(), t[1].item(), int(t[2].item()), t[3].item()
     assert status == 0, f"a kernel reported device status {status}"
 
     if rank == 0:
@@ -299,12 +325,37 @@ def run_ours(args) -> None:
                          "kernel": "w4_stream_kernel", "bytes_per_launch": int(per_launch_bytes)},
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches_per_step * args.steps,
+            "tp_stack": {"workload": "llama3_8b_projection_stack_int4 (32 layers x qkv,o,gate_up,down; M=64)",
+                         "value": round(stack.bytes_per_pass() * args.steps / (ms_stack * 1e-3) / 1e9, 2), "unit": "GB/s",
+                         "ms_per_pass": round(ms_stack / args.steps, 4), "parallelism": f"tp{tp}",
+                         "allreduces_per_pass": 0 if world == 1 else 2 * 32, "launches_per_pass": stack.launches_per_pass},
+            "gpu_launches": (launches_per_step + stack.launches_per_pass) * args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_one_gemm(args) -> None:
+    """A small case for ncu: one shape, 4 weight copies (larger than L2 together for the Llama
+    shapes), 6 launches through the public op."""
+    import torch
+
+    import spark_kernels as sk
+
+    K, N, M = (int(v) for v in args.one_gemm.split(","))
+    torch.cuda.set_device(0)
+    sk._C.init()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ws = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 16, 2 * K), dtype=torch.int32, device="cuda", generator=g),
+           (torch.rand(K // 128, N, device="cuda", generator=g) * 0.02).to(torch.bfloat16)) for _ in range(4)]
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(6):
+        sk.w4gemm(a, ws[i % 4][0], ws[i % 4][1], None, -1, out)
+    torch.cuda.synchronize()
+    print(json.dumps({"one_gemm": [K, N, M], "status": sk._C.device_status()}))
 
 
 def main() -> None:
@@ -314,8 +365,12 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--one-gemm", default="", metavar="K,N,M",
+                    help="profiling helper: run a few launches of one w4gemm shape over 4 weight copies and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.one_gemm:
+        run_one_gemm(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)
