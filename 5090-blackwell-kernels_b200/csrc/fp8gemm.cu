@@ -24,7 +24,6 @@ bool tensor_core_shape(int M, int N, int K, int sms) {
 }
 
 int sm_count_or(int fallback) {
-    DeviceState* d = nullptr;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -35,7 +34,6 @@ int sm_count_or(int fallback) {
         (void)cudaGetLastError();
         return fallback;
     }
-    (void)d;
     return sms;
 }
 

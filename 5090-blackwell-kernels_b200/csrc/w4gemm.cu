@@ -34,8 +34,6 @@ using ptx::mbar_arrive_expect_tx;
 using ptx::mbar_init;
 using ptx::mbar_wait;
 
-__host__ __device__ constexpr int cdiv_c(int a, int b) { return (a + b - 1) / b; }
-
 // ---- variant 0 ----------------------------------------------------------------------------------
 
 __global__ void w4_naive_kernel(const __nv_bfloat16* __restrict__ A, const uint32_t* __restrict__ packed,
