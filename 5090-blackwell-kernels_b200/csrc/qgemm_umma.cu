@@ -1,0 +1,342 @@
+// Tensor-core route of the fp8 and fp4 GEMMs: one TMA-fed tcgen05 kernel, accumulator in TMEM,
+// in four operand modes
+//   kFp8     e4m3 x e4m3, per-tensor scales              tcgen05.mma.kind::f8f6f4
+//   kFp8Mx   e4m3 x e4m3, ue8m0 scale per 32 k           kind::mxf8f6f4.block_scale
+//   kNvfp4   e2m1 x e2m1, e4m3 scale per 16 k            kind::mxf4nvf4.block_scale.scale_vec::4X
+//   kMxfp4   e2m1 x e2m1, ue8m0 scale per 32 k           kind::mxf4nvf4.block_scale.scale_vec::2X
+//
+// One CTA computes one 128 x BN tile of C. Roles, one warp each unless noted:
+//   warp 0   producer: per K block (128 bytes of K per row) one thread issues two tiled TMA loads
+//            (A 128 x 128 B, Bt BN x 128 B, 128-byte swizzle) and, in the block-scaled modes, bulk
+//            copies of the 512-byte scale tiles (128 rows x 4 scales, the blocked layout of the
+//            API, which is the layout the tensor core wants) into a ring of kStages stages
+//   warp 1   MMA: allocates TMEM; one thread copies the stage's scale tiles shared -> TMEM
+//            (tcgen05.cp), issues four MMAs (128 x BN x 32 bytes of K) and commits them to the
+//            stage's "empty" barrier, and at the end to the "accumulator ready" barrier
+//   warps 2-5  epilogue: each reads the 32 accumulator rows of its TMEM quarter (tcgen05.ld), applies
+//            scale_a * scale_b in fp32, rounds once to bf16 and stores
+// Rows past M, columns past N and k past K are zero-filled by TMA, so any shape the API accepts
+// runs; the stores are predicated. Every barrier wait is bounded; on a timeout the roles stop,
+// the status word is set, and TMEM is still released.
+#include "qgemm_simt.cuh"
+#include "umma_sm100.cuh"
+
+namespace spk {
+namespace {
+
+using ptx::bulk_g2s;
+using ptx::mbar_arrive_expect_tx;
+using ptx::mbar_init;
+using ptx::mbar_wait;
+
+enum UmmaMode { kFp8 = 0, kFp8Mx = 1, kNvfp4 = 2, kMxfp4 = 3 };
+
+constexpr int kBM = 128, kBKBytes = 128, kStages = 4;
+constexpr int kSfTile = 512;             // 128 rows x 4 scale bytes
+constexpr int kSfColsPerStage = 16 + 32;  // TMEM columns kept for one stage's scales (A: <= 16, B: <= 32)
+
+template <int MODE>
+struct ModeTraits {
+    static constexpr bool kScaled = MODE != kFp8;
+    // scale tiles per 128-row block per stage: MXFP8 1 (4 scales = 128 k), NVFP4 4 (one per MMA),
+    // MXFP4 2 (one per two MMAs)
+    static constexpr int kTiles = MODE == kFp8Mx ? 1 : MODE == kNvfp4 ? 4 : MODE == kMxfp4 ? 2 : 0;
+    static constexpr int kElemsPerByte = (MODE == kNvfp4 || MODE == kMxfp4) ? 2 : 1;
+};
+
+template <int BN, int MODE>
+struct UmmaCfg {
+    using T = ModeTraits<MODE>;
+    static constexpr int kABytes = kBM * kBKBytes, kBBytes = BN * kBKBytes;
+    static constexpr int kSfABytes = T::kTiles * kSfTile, kSfBBytes = (BN / 128) * T::kTiles * kSfTile;
+    static constexpr int kTxBytes = kABytes + kBBytes + kSfABytes + kSfBBytes;  // what lands per stage
+    static constexpr int kStageBytes = (kTxBytes + 1023) / 1024 * 1024;           // stages keep the tile alignment
+    static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int kTmemCols = T::kScaled ? 512 : BN;
+    static constexpr int kSfColBase = BN;  // scale columns follow the accumulator
+};
+
+struct UmmaParams {
+    __nv_bfloat16* C;
+    int M, N, K;  // K in elements
+    const float* scale_a;
+    const float* scale_b;
+    const unsigned char* sfa;  // blocked layout (all block-scaled modes)
+    const unsigned char* sfb;
+    int sf_tiles_per_rowblock;  // 512-byte tiles per 128-row block (K / 128, K / 64, K / 128)
+    int* status;
+};
+
+// Shared-memory descriptor of one 512-byte scale tile for tcgen05.cp: 32 rows of 16 bytes, no
+// swizzle (8-row core matrices of 128 contiguous bytes, 128 bytes apart).
+__device__ __forceinline__ uint64_t sf_desc(const void* tile) {
+    const uint64_t addr = (ptx::smem_u32(tile) & 0x3FFFFu) >> 4;
+    return addr | (uint64_t{128 >> 4} << 32) | (uint64_t{1} << 46);
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
+// Block-scaled instruction descriptor: formats at [7,10) and [10,13), N >> 3 at [17,23), scale
+// format (0 e4m3, 1 ue8m0) at bit 23, M >> 4 at [24,29), scale ids of B at [4,6) and of A at [29,31).
+__host__ __device__ constexpr uint32_t instr_desc_scaled(int m, int n, int fmt, int scale_fmt, int sf_id) {
+    return (static_cast<uint32_t>(sf_id) << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(scale_fmt) << 23) |
+           (static_cast<uint32_t>(m >> 4) << 24) | (static_cast<uint32_t>(sf_id) << 29);
+}
+
+template <int MODE>
+__device__ __forceinline__ void mma_scaled(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa,
+                                           uint32_t tsfb, bool accumulate) {
+    const uint32_t acc = accumulate;
+    if (MODE == kFp8Mx)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(tmem_d),
+                     "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(tsfa), "r"(tsfb)
+                     : "memory");
+    else if (MODE == kNvfp4)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(
+                         tmem_d),
+                     "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(tsfa), "r"(tsfb)
+                     : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(
+                         tmem_d),
+                     "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(tsfa), "r"(tsfb)
+                     : "memory");
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(192, 1)
+qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const UmmaParams p) {
+    using Cfg = UmmaCfg<BN, MODE>;
+    using T = ModeTraits<MODE>;
+    constexpr int NB = BN / 128;  // 128-row blocks of Bt per tile
+    extern __shared__ unsigned char smem_raw[];
+    // 128-byte-swizzled tiles must start on a 1024-byte boundary
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kStages * Cfg::kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_ready = empty + kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tile_m = blockIdx.x % tiles_m, tile_n = blockIdx.x / tiles_m;
+    const int k_bytes = p.K / T::kElemsPerByte;
+    const int k_blocks = (k_bytes + kBKBytes - 1) / kBKBytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_ready, 1);
+        ptx::fence_mbar_init();
+        umma::prefetch_tensormap(&map_a);
+        umma::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) umma::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                // a fresh barrier passes a wait on the opposite parity, so the first lap does not block
+                if (!mbar_wait(&empty[s], ((kb / kStages) & 1) ^ 1, p.status)) break;
+                mbar_arrive_expect_tx(&full[s], Cfg::kTxBytes);
+                unsigned char* st = tiles + s * Cfg::kStageBytes;
+                umma::tma_load_2d(st, &map_a, kb * kBKBytes, tile_m * kBM, &full[s]);
+                umma::tma_load_2d(st + Cfg::kABytes, &map_b, kb * kBKBytes, tile_n * BN, &full[s]);
+                if (T::kScaled) {
+                    unsigned char* sf = st + Cfg::kABytes + Cfg::kBBytes;
+                    const size_t tile0 = static_cast<size_t>(kb) * T::kTiles;
+                    bulk_g2s(sf, p.sfa + (static_cast<size_t>(tile_m) * p.sf_tiles_per_rowblock + tile0) * kSfTile,
+                             Cfg::kSfABytes, &full[s]);
+#pragma unroll
+                    for (int i = 0; i < NB; ++i)
+                        bulk_g2s(sf + Cfg::kSfABytes + i * (T::kTiles * kSfTile),
+                                 p.sfb + (static_cast<size_t>(tile_n * NB + i) * p.sf_tiles_per_rowblock + tile0) * kSfTile,
+                                 T::kTiles * kSfTile, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % kStages;
+                ok = mbar_wait(&full[s], (kb / kStages) & 1, p.status);
+                if (!ok) break;
+                umma::fence_after_sync();
+                const unsigned char* st = tiles + s * Cfg::kStageBytes;
+                const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + Cfg::kABytes);
+                if (!T::kScaled) {
+                    constexpr uint32_t idesc = umma::instr_desc(kBM, BN, 0, 0);  // e4m3 x e4m3 -> f32
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma::mma_f8f6f4(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
+                                         kb > 0 || k > 0);
+                } else {
+                    // this stage's scale tiles, shared -> TMEM: A tile t at columns sfa + 4 t; Bt row block i of
+                    // tile t at sfb + 4 (NB t + i), so the NB row blocks of one MMA sit side by side
+                    const unsigned char* sf = st + Cfg::kABytes + Cfg::kBBytes;
+                    const uint32_t sfa_col = tmem_acc + Cfg::kSfColBase + s * kSfColsPerStage, sfb_col = sfa_col + 16;
+#pragma unroll
+                    for (int t = 0; t < T::kTiles; ++t) {
+                        tmem_cp_sf(sfa_col + 4 * t, sf_desc(sf + t * kSfTile));
+#pragma unroll
+                        for (int i = 0; i < NB; ++i)
+                            tmem_cp_sf(sfb_col + 4 * (NB * t + i), sf_desc(sf + Cfg::kSfABytes + (i * T::kTiles + t) * kSfTile));
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // which scale tile and which bytes of its 32-bit words MMA k uses
+                        const int t = MODE == kNvfp4 ? k : MODE == kMxfp4 ? (k >> 1) : 0;
+                        const int sf_id = MODE == kNvfp4 ? 0 : MODE == kMxfp4 ? 2 * (k & 1) : k;
+                        const uint32_t idesc = instr_desc_scaled(kBM, BN, MODE == kFp8Mx ? 0 : 1, MODE == kNvfp4 ? 0 : 1, sf_id);
+                        mma_scaled<MODE>(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
+                                         sfa_col + 4 * t, sfb_col + 4 * NB * t, kb > 0 || k > 0);
+                    }
+                }
+                umma::mma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+            }
+            umma::mma_commit(acc_ready);  // fires after every MMA above has completed (also on failure)
+        }
+    } else {
+        // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1 ----
+        const int quarter = warp & 3;
+        const bool ok = mbar_wait(acc_ready, 0, p.status);
+        umma::fence_after_sync();
+        if (ok) {
+            const float s = (p.scale_a ? *p.scale_a : 1.0f) * (p.scale_b ? *p.scale_b : 1.0f);
+            const int row = tile_m * kBM + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                umma::tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, r);
+                umma::tmem_ld_wait();
+                const int col = tile_n * BN + c0;
+                if (row < p.M && col < p.N) {  // N % 64 == 0 and c0 % 32 == 0: a 32-column run is all in or all out
+                    uint4 out[4];
+                    uint32_t* o = reinterpret_cast<uint32_t*>(out);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * s, __uint_as_float(r[2 * j + 1]) * s);
+                        o[j] = *reinterpret_cast<const uint32_t*>(&v);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(p.C + static_cast<size_t>(row) * p.N + col);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = out[j];
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) umma::tmem_dealloc(tmem_acc, Cfg::kTmemCols);
+}
+
+template <int BN, int MODE>
+int launch_umma(const simt::Params& q, const unsigned char* sfa, const unsigned char* sfb, DeviceState* dev,
+                cudaStream_t stream) {
+    using Cfg = UmmaCfg<BN, MODE>;
+    using T = ModeTraits<MODE>;
+    static_assert(Cfg::kStageBytes % 1024 == 0, "stages must keep the 1024-byte tile alignment");
+    static_assert(Cfg::kSmem <= 227 * 1024, "stage ring exceeds shared memory");
+    const uint64_t row_bytes = static_cast<uint64_t>(q.K) / T::kElemsPerByte;
+    CUtensorMap map_a, map_b;
+    if (!umma::make_map_2d_u8(&map_a, q.A, row_bytes, static_cast<uint64_t>(q.M), kBM) ||
+        !umma::make_map_2d_u8(&map_b, q.Bt, row_bytes, static_cast<uint64_t>(q.N), BN))
+        return fail(SPK_CUDA_ERROR, "umma gemm: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
+    auto kernel = qgemm_umma_kernel<BN, MODE>;
+    static bool configured[16] = {};
+    if (!configured[dev->device & 15]) {
+        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        configured[dev->device & 15] = true;
+    }
+    UmmaParams p{};
+    p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
+    p.scale_a = q.scale_a, p.scale_b = q.scale_b;
+    p.sfa = sfa, p.sfb = sfb;
+    p.sf_tiles_per_rowblock = MODE == kNvfp4 ? q.K / 64 : q.K / 128;
+    p.status = dev->status;
+    const int grid = cdiv(q.M, kBM) * cdiv(q.N, BN);
+    kernel<<<grid, 192, Cfg::kSmem, stream>>>(map_a, map_b, p);
+    SPK_CHECK_LAUNCH();
+    return SPK_OK;
+}
+
+// Row-major ue8m0 scales [rows][K/32] (the fp8 MX API layout) -> the blocked layout the tensor core
+// reads, rows padded to 128 with zero bytes. One thread per 4 scales (one 32-bit word).
+__global__ void __launch_bounds__(256)
+mx_scales_to_blocked_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, int rows, int cols,
+                            long long words) {
+    const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= words) return;
+    const int wpr = cols / 4;
+    const int r = static_cast<int>(i / wpr), jw = static_cast<int>(i % wpr);
+    const unsigned v = r < rows ? *reinterpret_cast<const unsigned*>(src + static_cast<size_t>(r) * cols + 4 * jw) : 0u;
+    *reinterpret_cast<unsigned*>(dst + fp::sf_offset(r, 4 * jw, cols)) = v;
+}
+
+bool umma_disabled() {
+    const char* e = std::getenv("SPK_NO_UMMA");
+    return e && *e == '1';
+}
+
+}  // namespace
+
+// Variant 3 (and 2) of fp8gemm: every shape with M > 64 runs on the tensor cores. In MX mode the
+// row-major scales are first rewritten into the blocked layout inside the per-device scratch.
+int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t stream, bool* taken) {
+    *taken = false;
+    (void)variant;
+    if (p.M <= 64 || !aligned16(p.C) || umma_disabled()) return SPK_OK;
+    DeviceState* dev = nullptr;
+    if (int rc = device_state(&dev)) return rc;
+    if (!mx) {
+        *taken = true;
+        return p.N % 256 == 0 ? launch_umma<256, kFp8>(p, nullptr, nullptr, dev, stream)
+                              : launch_umma<128, kFp8>(p, nullptr, nullptr, dev, stream);
+    }
+    const int cols = p.K / 32;
+    const size_t a_bytes = static_cast<size_t>(cdiv(p.M, 128)) * 128 * cols, b_bytes = static_cast<size_t>(cdiv(p.N, 128)) * 128 * cols;
+    if (a_bytes + b_bytes > static_cast<size_t>(kPartialFloats) * sizeof(float)) return SPK_OK;  // scratch too small
+    *taken = true;
+    unsigned char* sfa = reinterpret_cast<unsigned char*>(dev->partials);
+    unsigned char* sfb = sfa + a_bytes;
+    const long long wa = static_cast<long long>(a_bytes / 4), wb = static_cast<long long>(b_bytes / 4);
+    mx_scales_to_blocked_kernel<<<static_cast<unsigned>(cdiv64(wa, 256)), 256, 0, stream>>>(p.sfa, sfa, p.M, cols, wa);
+    mx_scales_to_blocked_kernel<<<static_cast<unsigned>(cdiv64(wb, 256)), 256, 0, stream>>>(p.sfb, sfb, p.N, cols, wb);
+    SPK_CHECK_LAUNCH();
+    const int rc = p.N % 256 == 0 ? launch_umma<256, kFp8Mx>(p, sfa, sfb, dev, stream)
+                                  : launch_umma<128, kFp8Mx>(p, sfa, sfb, dev, stream);
+    if (rc != SPK_OK) return rc;
+    // the scratch is shared with the split-K kernels, which expect it zeroed
+    SPK_CUDA(cudaMemsetAsync(sfa, 0, a_bytes + b_bytes, stream));
+    return SPK_OK;
+}
+
+// Variant 2 of fp4gemm (M and N multiples of 128 by its rule).
+int fp4gemm_umma_try(const simt::Params& p, int format, cudaStream_t stream, bool* taken) {
+    *taken = false;
+    if (p.M % 128 != 0 || p.N % 128 != 0 || !aligned16(p.C) || umma_disabled()) return SPK_OK;
+    DeviceState* dev = nullptr;
+    if (int rc = device_state(&dev)) return rc;
+    *taken = true;
+    if (format == SPK_FP4_NVFP4)
+        return p.N % 256 == 0 ? launch_umma<256, kNvfp4>(p, p.sfa, p.sfb, dev, stream)
+                              : launch_umma<128, kNvfp4>(p, p.sfa, p.sfb, dev, stream);
+    return p.N % 256 == 0 ? launch_umma<256, kMxfp4>(p, p.sfa, p.sfb, dev, stream)
+                          : launch_umma<128, kMxfp4>(p, p.sfa, p.sfb, dev, stream);
+}
+
+}  // namespace spk

@@ -9,8 +9,10 @@ from tests.parity import assert_bf16_close, bf16_from_bits, t2n
 
 pytestmark = pytest.mark.gpu
 
+# the last two have at least one 128 x 128 tile per SM, which variant 2 (tensor cores) asks for:
+# one with N % 256 == 0 (128 x 256 tiles) and one without (128 x 128 tiles)
 SHAPES = [(16, 64, 256), (1, 128, 256), (5, 64, 512), (64, 256, 1024), (100, 128, 256), (16, 4096, 4096),
-          (128, 256, 512), (256, 512, 1024)]
+          (128, 256, 512), (256, 512, 1024), (2048, 2560, 512), (1536, 1664, 256)]
 
 
 @pytest.mark.parametrize("rows,K", [(1, 256), (100, 1024), (128, 4096), (300, 14336)])
@@ -74,7 +76,7 @@ def test_fp4gemm_variants_bit_equal_on_exact_sums(sk, orc, fmt):
     """Sums of e2m1 x block-scale products are exact in fp32 at this size, so every variant and
     the oracle give the same bits; block scales vary per block to catch a misrouted scale byte
     (reference tests/test_fp4gemm.py:111-146)."""
-    M, N, K = 128, 256, 512
+    M, N, K = 2048, 2560, 512
     (qa, sfa, sa), (qb, sfb, sb) = _inputs(orc, M, N, K, fmt, 77)
     want = orc.fp4gemm(qa, qb, sfa, sfb, 1.0, 1.0, fmt)
     for v in (0, 1, 2):

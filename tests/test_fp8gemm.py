@@ -96,7 +96,8 @@ def test_fp8gemm_golden(sk, golden):
     assert_bf16_close(got, g["mxg_c"], "golden mx")
 
 
-MX_SHAPES = [(16, 64, 256), (1, 128, 512), (5, 64, 256), (64, 256, 1024), (128, 256, 512), (16, 4096, 4096)]
+MX_SHAPES = [(16, 64, 256), (1, 128, 512), (5, 64, 256), (64, 256, 1024), (128, 256, 512), (16, 4096, 4096),
+             (256, 384, 512), (300, 512, 768)]
 
 
 def _mx_inputs(orc, M, N, K, seed):
