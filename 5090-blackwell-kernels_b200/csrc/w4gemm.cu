@@ -626,6 +626,12 @@ int launch_stream(const StreamParams& p, bool whole, const DeviceState& dev, cud
 }  // namespace
 }  // namespace spk
 
+namespace spk {
+// defined in w4gemm_umma.cu
+int w4gemm_umma_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
+                    int K, cudaStream_t stream, bool* taken);
+}  // namespace spk
+
 extern "C" int spk_w4gemm_num_variants(void) { return 4; }
 extern "C" int spk_w4gemm_default_variant(void) { return 2; }
 extern "C" int spk_w4gemm_supports(int M, int N, int K, int variant) {
@@ -661,6 +667,11 @@ extern "C" int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void*
             w4_strip_kernel<false><<<grid, 128, 0, stream>>>(a, reinterpret_cast<const uint4*>(packed), sc, zeros, c, M, N, K);
         SPK_CHECK_LAUNCH();
         return SPK_OK;
+    }
+    if (variant == 2) {  // the tensor-core route for mid-size token counts
+        bool taken = false;
+        const int rc = w4gemm_umma_try(A, packed, scales, zeros, C, M, N, K, stream, &taken);
+        if (taken || rc != SPK_OK) return rc;
     }
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;

@@ -334,7 +334,15 @@ def run_ours(args) -> None:
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Captured graphs hold NCCL work; tearing the process group down with them alive was seen to
+        # block forever on this software stack. Drop them, line the ranks up, and leave without the
+        # interpreter's teardown.
+        del graph, sgraph
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def run_one_gemm(args) -> None:
