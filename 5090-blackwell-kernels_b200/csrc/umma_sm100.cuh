@@ -95,6 +95,14 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "r"(0u)
         : "memory");
 }
+// True in exactly one lane of a fully converged warp. The MMA warp runs its loop warp-wide and puts
+// only the tcgen05 instructions under this predicate: descriptors and loop state then stay provably
+// uniform, which a loop under `if (lane == 0)` does not allow (measured: ~70 cycles per MMA issue there).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+    return pred != 0;
+}
 // Arrive (count 1) on `bar` once every MMA this thread issued before has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ptx::smem_u32(bar))

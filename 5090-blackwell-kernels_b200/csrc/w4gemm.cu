@@ -511,6 +511,16 @@ w4_stream_kernel(const StreamParams p) {
             done = __shfl_sync(0xffffffffu, done, 0);
             if (done + static_cast<unsigned>(pend_n[i]) == static_cast<unsigned>(chunks)) {
                 __threadfence();
+                // every load first, so the tail costs one round trip and not MT * 4 of them
+                float v[MT][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = tok0 + 8 * mt + 2 * c + (e & 1);
+                        const int n = 16 * t + gl + 8 * (e >> 1);
+                        v[mt][e] = tok < p.M ? __ldcg(p.partials + static_cast<size_t>(tok) * p.N + n) : 0.f;
+                    }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -518,9 +528,8 @@ w4_stream_kernel(const StreamParams p) {
                         const int tok = tok0 + 8 * mt + 2 * c + (e & 1);
                         const int n = 16 * t + gl + 8 * (e >> 1);
                         if (tok < p.M) {
-                            float* cell = p.partials + static_cast<size_t>(tok) * p.N + n;
-                            p.C[static_cast<size_t>(tok) * p.N + n] = __float2bfloat16_rn(__ldcg(cell));
-                            __stcg(cell, 0.f);
+                            p.C[static_cast<size_t>(tok) * p.N + n] = __float2bfloat16_rn(v[mt][e]);
+                            __stcg(p.partials + static_cast<size_t>(tok) * p.N + n, 0.f);
                         }
                     }
                 if (lane == 0) *counter = 0u;

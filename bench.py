@@ -49,6 +49,16 @@ def alg_bytes(M: int, N: int, K: int) -> int:
     return 2 * M * K + K * N // 2 + 2 * (K // 128) * N + 2 * M * N
 
 
+def kernel_for(m: int) -> str:
+    """The kernel the default route launches for m tokens (w4gemm.cu / w4gemm_umma.cu)."""
+    return "w4_umma_kernel" if 16 < m <= 64 else "w4_stream_kernel"
+
+
+# DRAM bytes moved per algorithmic byte, from one ncu capture per kernel (dram__bytes_read.sum +
+# dram__bytes_write.sum over the launch's algorithmic bytes; the captures are summarised under profiles/).
+NCU_TRAFFIC_RATIO = {}
+
+
 def step_bytes(layers: int) -> int:
     return layers * sum(alg_bytes(m, 2 * INTER, HIDDEN) + alg_bytes(m, HIDDEN, INTER) for m in MS)
 
@@ -192,28 +202,37 @@ def run_ours(args) -> None:
     y_dn = {m: torch.empty(m, HIDDEN, device=dev, dtype=torch.bfloat16) for m in MS}
     launches_per_step = 0
 
-    def step():
+    def step_m(m):
         n = 0
-        for m in MS:
-            for layer in range(LAYERS):
-                sk.w4gemm(x[m], gu[layer][0], gu[layer][1], None, -1, y_gu[m])
-                sk.w4gemm(h[m], dn[layer][0], dn[layer][1], None, -1, y_dn[m])
-                n += 2
-                if world > 1:
-                    dist.all_reduce(y_dn[m])
+        for layer in range(LAYERS):
+            sk.w4gemm(x[m], gu[layer][0], gu[layer][1], None, -1, y_gu[m])
+            sk.w4gemm(h[m], dn[layer][0], dn[layer][1], None, -1, y_dn[m])
+            n += 2
+            if world > 1:
+                dist.all_reduce(y_dn[m])
         return n
 
-    # eager warm-up on a side stream, then capture one step
+    # eager warm-up on a side stream, then capture one graph per token count; a step replays all of them
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        launches_per_step = step()
+        launches_per_step = sum(step_m(m) for m in MS)
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        step()
+    graphs = {}
+    for m in MS:
+        graphs[m] = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graphs[m]):
+            step_m(m)
     torch.cuda.synchronize()
+
+    class _Step:
+        @staticmethod
+        def replay():
+            for m in MS:
+                graphs[m].replay()
+
+    graph = _Step
 
     def barrier():
         if world > 1:
@@ -235,6 +254,18 @@ def run_ours(args) -> None:
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)
+
+    # the same launches timed per token count (the roofline of the dominant kernel comes from here)
+    ms_by_m = {}
+    for m in MS:
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(args.steps):
+            graphs[m].replay()
+        g1.record()
+        barrier()
+        ms_by_m[m] = g0.elapsed_time(g1) / args.steps
 
     # end to end: activations from pinned host memory every step, outputs read back every step
     pin_x = {m: torch.randn(m, HIDDEN).to(torch.bfloat16).pin_memory() for m in MS}
@@ -304,9 +335,16 @@ def run_ours(args) -> None:
         value = total_bytes * args.steps / (ms_total * 1e-3) / 1e9
         e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
         peak, which = measured_peak()
-        per_launch_bytes = total_bytes / tp / launches_per_step
-        per_launch_ms = ms_total / args.steps / launches_per_step
-        achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
+        # per token count: algorithmic bytes of this rank's launches over their measured time; the
+        # dominant kernel is the one behind the token count with the largest share of the step
+        by_m = {}
+        for m in MS:
+            b = LAYERS * (alg_bytes(m, 2 * INTER // tp, HIDDEN) + alg_bytes(m, HIDDEN, INTER // tp))
+            by_m[m] = {"kernel": kernel_for(m), "launches": 2 * LAYERS, "us_per_launch": round(ms_by_m[m] * 1e3 / (2 * LAYERS), 2),
+                       "gbps": round(b / (ms_by_m[m] * 1e-3) / 1e9, 1), "bytes_per_launch": b // (2 * LAYERS)}
+        top = max(MS, key=lambda m: ms_by_m[m])
+        achieved = by_m[top]["gbps"]
+        traffic = NCU_TRAFFIC_RATIO.get(by_m[top]["kernel"])
         cpu = None
         if world == 1 and not args.no_cpu:
             gbs, secs, used, sample = cpu_sample(0)
@@ -320,9 +358,12 @@ def run_ours(args) -> None:
             "config": {"workload": WORKLOAD, "layers": LAYERS, "M": list(MS), "gate_up": [2 * INTER, HIDDEN],
                        "down": [HIDDEN, INTER], "group": 128, "parallelism": f"tp{tp}",
                        "l2": "inputs larger than L2 (1.4 GB of weights per step)", "launch": "cuda graph"},
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "peak_source": which, "traffic": None,
-                         "kernel": "w4_stream_kernel", "bytes_per_launch": int(per_launch_bytes)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_source": which,
+                         "traffic": None if traffic is None or tp > 1 else int(traffic * by_m[top]["bytes_per_launch"]),
+                         "kernel": by_m[top]["kernel"], "tokens": top, "bytes_per_launch": by_m[top]["bytes_per_launch"],
+                         "share_of_step": round(ms_by_m[top] / sum(ms_by_m.values()), 3),
+                         "by_tokens": {str(m): by_m[m] for m in MS}},
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "tp_stack": {"workload": "llama3_8b_projection_stack_int4 (32 layers x qkv,o,gate_up,down; M=64)",
@@ -337,7 +378,8 @@ def run_ours(args) -> None:
         # Captured graphs hold NCCL work; tearing the process group down with them alive was seen to
         # block forever on this software stack. Drop them, line the ranks up, and leave without the
         # interpreter's teardown.
-        del graph, sgraph
+        graphs.clear()
+        del sgraph
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
@@ -346,24 +388,56 @@ def run_ours(args) -> None:
 
 
 def run_one_gemm(args) -> None:
-    """A small case for ncu: one shape, 4 weight copies (larger than L2 together for the Llama
-    shapes), 6 launches through the public op."""
+    """A small case for ncu and for the secondary GEMMs: one shape through the public op, a few
+    launches, timed with CUDA events. w4: K,N,M over 4 weight copies (larger than L2 together for the
+    Llama shapes). fp8 / mxfp8 / nvfp4 / mxfp4: M,N,K of a square-ish compute-bound GEMM."""
     import torch
 
     import spark_kernels as sk
 
-    K, N, M = (int(v) for v in args.one_gemm.split(","))
+    d0, d1, d2 = (int(v) for v in args.one_gemm.split(","))
     torch.cuda.set_device(0)
     sk._C.init()
     g = torch.Generator(device="cuda").manual_seed(0)
-    ws = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 16, 2 * K), dtype=torch.int32, device="cuda", generator=g),
-           (torch.rand(K // 128, N, device="cuda", generator=g) * 0.02).to(torch.bfloat16)) for _ in range(4)]
-    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
-    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    for i in range(6):
-        sk.w4gemm(a, ws[i % 4][0], ws[i % 4][1], None, -1, out)
+    if args.kind == "w4":
+        K, N, M = d0, d1, d2
+        ws = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 16, 2 * K), dtype=torch.int32, device="cuda", generator=g),
+               (torch.rand(K // 128, N, device="cuda", generator=g) * 0.02).to(torch.bfloat16)) for _ in range(4)]
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        calls = [lambda i=i: sk.w4gemm(a, ws[i % 4][0], ws[i % 4][1], None, -1, out) for i in range(4)]
+        work, unit = alg_bytes(M, N, K), "GB/s"
+    else:
+        M, N, K = d0, d1, d2
+        a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+        if args.kind == "fp8":
+            (qa, sa), (qb, sb) = sk.fp8_quantize(a, "tensor"), sk.fp8_quantize(b, "tensor")
+            calls = [lambda: sk.fp8gemm(qa, qb, sa, sb)]
+        elif args.kind == "mxfp8":
+            (qa, sfa), (qb, sfb) = sk.fp8_quantize(a, "mx"), sk.fp8_quantize(b, "mx")
+            calls = [lambda: sk.fp8gemm(qa, qb, sfa=sfa, sfb=sfb)]
+        else:
+            qa, sfa, sa = sk.fp4_quantize(a, args.kind)
+            qb, sfb, sb = sk.fp4_quantize(b, args.kind)
+            kw = {} if args.kind == "mxfp4" else {"scale_a": sa.reshape(1), "scale_b": sb.reshape(1)}
+            calls = [lambda: sk.fp4gemm(qa, qb, sfa, sfb, fmt=args.kind, **kw)]
+        work, unit = 2 * M * N * K, "TFLOP/s"
+    for i in range(3):
+        calls[i % len(calls)]()
     torch.cuda.synchronize()
-    print(json.dumps({"one_gemm": [K, N, M], "status": sk._C.device_status()}))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = max(1, args.steps)
+    e0.record()
+    for i in range(n):
+        calls[i % len(calls)]()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    print(json.dumps({"one_gemm": [d0, d1, d2], "kind": args.kind, "launches": 3 + n, "us_per_launch": round(ms * 1e3, 2),
+                      "rate": round(rate, 1), "unit": unit, "timing": "eager launches, CUDA events",
+                      "status": sk._C.device_status()}))
 
 
 def main() -> None:
@@ -373,8 +447,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--one-gemm", default="", metavar="K,N,M",
-                    help="profiling helper: run a few launches of one w4gemm shape over 4 weight copies and exit")
+    ap.add_argument("--one-gemm", default="", metavar="A,B,C",
+                    help="profiling helper: run --steps launches of one GEMM shape through the public op and exit")
+    ap.add_argument("--kind", default="w4", choices=["w4", "fp8", "mxfp8", "nvfp4", "mxfp4"],
+                    help="with --one-gemm: which GEMM (w4 takes K,N,M; the others M,N,K)")
     args = ap.parse_args()
     if args.one_gemm:
         run_one_gemm(args)
