@@ -169,13 +169,17 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The loop runs warp-wide so that stage indices and descriptors stay uniform; one elected lane
+        // issues the tcgen05 instructions (always the same lane, so its commits cover its MMAs).
+        {
             bool ok = true;
+            int s = 0;
+            unsigned ph = 0;
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % kStages;
-                ok = mbar_wait(&full[s], (kb / kStages) & 1, p.status);
+                ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, p.status));
                 if (!ok) break;
                 umma::fence_after_sync();
+                if (umma::elect_one()) {
                 const unsigned char* st = tiles + s * Cfg::kStageBytes;
                 const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + Cfg::kABytes);
                 if (!T::kScaled) {
@@ -207,8 +211,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                 }
                 umma::mma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                }
+                __syncwarp();
+                if (++s == kStages) s = 0, ph ^= 1u;
             }
-            umma::mma_commit(acc_ready);  // fires after every MMA above has completed (also on failure)
+            if (umma::elect_one()) umma::mma_commit(acc_ready);  // fires after every MMA above has completed (also on failure)
+            __syncwarp();
         }
     } else {
         // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1 ----
