@@ -56,7 +56,7 @@ def kernel_for(m: int) -> str:
 
 # DRAM bytes moved per algorithmic byte, from one ncu capture per kernel (dram__bytes_read.sum +
 # dram__bytes_write.sum over the launch's algorithmic bytes; the captures are summarised under profiles/).
-NCU_TRAFFIC_RATIO = {}
+NCU_TRAFFIC_RATIO = {"w4_umma_kernel": 1.031, "w4_stream_kernel": 1.005}
 
 
 def step_bytes(layers: int) -> int:
@@ -120,8 +120,8 @@ class ClockSampler:
 # ---- CPU arm -------------------------------------------------------------------------------------
 
 def cpu_sample(threads: int = 0):
-    """One bounded sample of the workload on the host: one layer's gate|up and down at M = 1, 16
-    (the M = 64 pair alone is 11 G multiply-adds; it is left out to keep the sample near 10-20 s).
+    """One bounded sample of the workload on the host: one of the 16 layers, gate|up and down at
+    every token count of the GPU arm (M = 1, 16, 64), all host threads.
     Returns (GB/s of algorithmic bytes, seconds, threads, description)."""
     import numpy as np
 
@@ -129,7 +129,7 @@ def cpu_sample(threads: int = 0):
 
     orc.lib()
     rng = np.random.default_rng(0)
-    ms = (1, 16)
+    ms = MS
     total, secs = 0, 0.0
     for (K, N) in ((HIDDEN, 2 * INTER), (INTER, HIDDEN)):
         packed = rng.integers(-2 ** 31, 2 ** 31 - 1, size=(N // 16, 2 * K), dtype=np.int64).astype(np.int32)
@@ -141,7 +141,7 @@ def cpu_sample(threads: int = 0):
             secs += time.perf_counter() - t0
             total += alg_bytes(M, N, K)
     used = threads if threads > 0 else orc.max_threads()
-    return total / secs / 1e9, secs, used, "1 layer: gate|up 28672x4096 and down 4096x14336 at M=1,16"
+    return total / secs / 1e9, secs, used, "1 of 16 layers: gate|up 28672x4096 and down 4096x14336 at M=1,16,64"
 
 
 def run_reference_arm(args) -> None:
