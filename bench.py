@@ -128,6 +128,9 @@ def cpu_sample(threads: int = 0):
     from oracle import oracle as orc
 
     orc.lib()
+    if threads <= 0:
+        # every core this process may run on; a launcher's OMP_NUM_THREADS=1 default must not shrink it
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     rng = np.random.default_rng(0)
     ms = MS
     total, secs = 0, 0.0
@@ -140,7 +143,7 @@ def cpu_sample(threads: int = 0):
             orc.w4gemm(a, packed, scales, None, threads=threads)
             secs += time.perf_counter() - t0
             total += alg_bytes(M, N, K)
-    used = threads if threads > 0 else orc.max_threads()
+    used = threads
     return total / secs / 1e9, secs, used, "1 of 16 layers: gate|up 28672x4096 and down 4096x14336 at M=1,16,64"
 
 
