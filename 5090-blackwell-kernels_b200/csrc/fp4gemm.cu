@@ -56,7 +56,7 @@ extern "C" int spk_fp4gemm(const void* A, const void* Bt, void* C, int M, int N,
     p.M = M, p.N = N, p.K = K;
     p.scale_a = scale_a, p.scale_b = scale_b;
     p.sfa = sfa, p.sfb = sfb;
-    if (variant == 2) {
+    if (variant == 2 || (variant == 1 && M <= 64)) {  // tensor-core routes: large tiles, and decode with split-K
         bool taken = false;
         const int rc = fp4gemm_umma_try(p, format, stream, &taken);
         if (taken || rc != SPK_OK) return rc;

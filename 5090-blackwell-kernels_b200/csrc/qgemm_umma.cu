@@ -18,6 +18,8 @@
 // Rows past M, columns past N and k past K are zero-filled by TMA, so any shape the API accepts
 // runs; the stores are predicated. Every barrier wait is bounded; on a timeout the roles stop,
 // the status word is set, and TMEM is still released.
+#include <algorithm>
+
 #include "qgemm_simt.cuh"
 #include "umma_sm100.cuh"
 
@@ -282,6 +284,255 @@ int launch_umma(const simt::Params& q, const unsigned char* sfa, const unsigned 
     return SPK_OK;
 }
 
+// ---- decode shapes (M <= 64): weights as the 128-row operand, split-K ------------------------------
+//
+// D[n][m] (TMEM, 128 x NT fp32) += Bt[n][k] (smem) * A[m][k] (smem): the weight rows fill the 128
+// lanes of the MMA and the few tokens are its N (16 / 32 / 64, rows past M zero-filled by TMA), so
+// no tensor-core work is spent on padding tokens. The GEMM is a read-once stream of the weights:
+// K is split over as many CTAs as fill the SMs once, every CTA keeps kDecodeStages stages of TMA
+// loads in flight, and the partial tiles are summed in the fp32 scratch (atomics, per-(tile,
+// quarter) counters, the last arriver converts and re-zeroes). The output is written transposed:
+// a lane holds one n for all m, and for each m a warp stores 32 consecutive n.
+constexpr int kDecodeStages = 6;
+
+template <int NT, int MODE>
+struct DecodeCfg {
+    using T = ModeTraits<MODE>;
+    static constexpr int kWBytes = kBM * kBKBytes, kXBytes = NT * kBKBytes;
+    static constexpr int kSfBytes = T::kTiles * kSfTile;  // per operand
+    static constexpr int kTxBytes = kWBytes + kXBytes + 2 * kSfBytes;
+    static constexpr int kStageBytes = (kTxBytes + 1023) / 1024 * 1024;
+    static constexpr int kSmem = kDecodeStages * kStageBytes + 1024 + 256;
+    static constexpr int kSfColBase = 64, kSfColsPerStage = 32;  // weights' scales at +0, tokens' at +16
+    static constexpr int kTmemCols = T::kScaled ? 256 : (NT < 32 ? 32 : NT);
+    static_assert(!T::kScaled || kSfColBase + kDecodeStages * kSfColsPerStage <= 256, "TMEM columns");
+};
+
+struct DecodeParams {
+    __nv_bfloat16* C;
+    int M, N, K;  // K in elements
+    const float* scale_a;
+    const float* scale_b;
+    const unsigned char* sfw;  // blocked scales of the weights (Bt) and of the tokens (A)
+    const unsigned char* sfx;
+    int sf_tiles_per_rowblock;
+    int n_tiles, split;
+    float* partials;
+    unsigned* counters;
+    int* status;
+};
+
+template <int NT, int MODE>
+__global__ void __launch_bounds__(192, 2)
+qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                         const DecodeParams p) {
+    using Cfg = DecodeCfg<NT, MODE>;
+    using T = ModeTraits<MODE>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kDecodeStages * Cfg::kStageBytes);
+    uint64_t* empty = full + kDecodeStages;
+    uint64_t* acc_ready = empty + kDecodeStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x % p.n_tiles, sk = blockIdx.x / p.n_tiles;
+    const int k_bytes = p.K / T::kElemsPerByte;
+    const int k_blocks_all = (k_bytes + kBKBytes - 1) / kBKBytes;
+    const int kb0 = static_cast<int>(static_cast<long long>(sk) * k_blocks_all / p.split);
+    const int kb1 = static_cast<int>(static_cast<long long>(sk + 1) * k_blocks_all / p.split);
+
+    if (threadIdx.x < 2 * kDecodeStages) mbar_init(&full[threadIdx.x], 1);  // full[] and empty[] are contiguous
+    if (threadIdx.x == 2 * kDecodeStages) {
+        mbar_init(acc_ready, 1);
+        umma::prefetch_tensormap(&map_w);
+        umma::prefetch_tensormap(&map_x);
+    }
+    ptx::fence_mbar_init();
+    if (warp == 1) umma::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    if (warp == 0) {
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            // a fresh barrier passes a wait on the opposite parity, so the first lap does not block
+            ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, p.status));
+            if (!ok) break;
+            if (umma::elect_one()) {
+                mbar_arrive_expect_tx(&full[s], Cfg::kTxBytes);
+                unsigned char* st = tiles + s * Cfg::kStageBytes;
+                umma::tma_load_2d(st, &map_w, kb * kBKBytes, tile_n * kBM, &full[s]);
+                umma::tma_load_2d(st + Cfg::kWBytes, &map_x, kb * kBKBytes, 0, &full[s]);
+                if (T::kScaled) {
+                    unsigned char* sf = st + Cfg::kWBytes + Cfg::kXBytes;
+                    const size_t tile0 = static_cast<size_t>(kb) * T::kTiles;
+                    bulk_g2s(sf, p.sfw + (static_cast<size_t>(tile_n) * p.sf_tiles_per_rowblock + tile0) * kSfTile, Cfg::kSfBytes,
+                             &full[s]);
+                    bulk_g2s(sf + Cfg::kSfBytes, p.sfx + tile0 * kSfTile, Cfg::kSfBytes, &full[s]);
+                }
+            }
+            __syncwarp();
+            if (++s == kDecodeStages) s = 0, ph ^= 1u;
+        }
+    } else if (warp == 1) {
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
+            if (umma::elect_one()) {
+                const unsigned char* st = tiles + s * Cfg::kStageBytes;
+                const uint64_t wdesc = umma::smem_desc_k128(st), xdesc = umma::smem_desc_k128(st + Cfg::kWBytes);
+                if (!T::kScaled) {
+                    constexpr uint32_t idesc = umma::instr_desc(kBM, NT, 0, 0);  // e4m3 x e4m3 -> f32
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma::mma_f8f6f4(tmem_acc, umma::desc_advance(wdesc, 32 * k), umma::desc_advance(xdesc, 32 * k), idesc,
+                                         kb > kb0 || k > 0);
+                } else {
+                    const unsigned char* sf = st + Cfg::kWBytes + Cfg::kXBytes;
+                    const uint32_t sfw_col = tmem_acc + Cfg::kSfColBase + s * Cfg::kSfColsPerStage, sfx_col = sfw_col + 16;
+#pragma unroll
+                    for (int t = 0; t < T::kTiles; ++t) {
+                        tmem_cp_sf(sfw_col + 4 * t, sf_desc(sf + t * kSfTile));
+                        tmem_cp_sf(sfx_col + 4 * t, sf_desc(sf + Cfg::kSfBytes + t * kSfTile));
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int t = MODE == kNvfp4 ? k : MODE == kMxfp4 ? (k >> 1) : 0;
+                        const int sf_id = MODE == kNvfp4 ? 0 : MODE == kMxfp4 ? 2 * (k & 1) : k;
+                        const uint32_t idesc = instr_desc_scaled(kBM, NT, MODE == kFp8Mx ? 0 : 1, MODE == kNvfp4 ? 0 : 1, sf_id);
+                        mma_scaled<MODE>(tmem_acc, umma::desc_advance(wdesc, 32 * k), umma::desc_advance(xdesc, 32 * k), idesc,
+                                         sfw_col + 4 * t, sfx_col + 4 * t, kb > kb0 || k > 0);
+                    }
+                }
+                umma::mma_commit(&empty[s]);
+            }
+            __syncwarp();
+            if (++s == kDecodeStages) s = 0, ph ^= 1u;
+        }
+        if (umma::elect_one()) umma::mma_commit(acc_ready);
+        __syncwarp();
+    } else {
+        // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1; lane = weight row n ----
+        const int quarter = warp & 3;
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0, p.status));
+        umma::fence_after_sync();
+        if (ok && kb1 > kb0) {
+            const float s = (p.scale_a ? *p.scale_a : 1.0f) * (p.scale_b ? *p.scale_b : 1.0f);
+            const int n = tile_n * kBM + quarter * 32 + lane;
+            uint32_t v[NT];
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                uint32_t r[16];
+                umma::tmem_ld_32x16(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, r);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[c0 + i] = r[i];
+            }
+            umma::tmem_ld_wait();
+            if (p.split == 1) {
+                if (n < p.N) {
+#pragma unroll
+                    for (int m = 0; m < NT; ++m)
+                        if (m < p.M) p.C[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[m]) * s);
+                }
+            } else {
+                if (n < p.N) {
+#pragma unroll
+                    for (int m = 0; m < NT; ++m)
+                        if (m < p.M) atomicAdd(p.partials + static_cast<size_t>(m) * p.N + n, __uint_as_float(v[m]) * s);
+                }
+                __threadfence();
+                __syncwarp();
+                unsigned done = 0;
+                unsigned* counter = p.counters + tile_n * 4 + quarter;
+                if (lane == 0) done = atomicAdd(counter, 1u);
+                done = __shfl_sync(0xffffffffu, done, 0);
+                if (done + 1 == static_cast<unsigned>(p.split)) {
+                    __threadfence();
+                    if (n < p.N) {
+                        for (int m0 = 0; m0 < p.M; m0 += 16) {  // loads of a batch in flight together
+                            float w[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                w[j] = m0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(m0 + j) * p.N + n) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (m0 + j < p.M) {
+                                    p.C[static_cast<size_t>(m0 + j) * p.N + n] = __float2bfloat16_rn(w[j]);
+                                    __stcg(p.partials + static_cast<size_t>(m0 + j) * p.N + n, 0.f);
+                                }
+                        }
+                    }
+                    if (lane == 0) *counter = 0u;
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) umma::tmem_dealloc(tmem_acc, Cfg::kTmemCols);
+}
+
+// sfw / sfx: blocked scales of Bt and A (null in the per-tensor mode); partials: M * N zeroed floats.
+template <int NT, int MODE>
+int launch_decode(const simt::Params& q, const unsigned char* sfw, const unsigned char* sfx, float* partials,
+                  DeviceState* dev, cudaStream_t stream) {
+    using Cfg = DecodeCfg<NT, MODE>;
+    using T = ModeTraits<MODE>;
+    static_assert(Cfg::kSmem <= 227 * 1024, "stage ring exceeds shared memory");
+    const uint64_t row_bytes = static_cast<uint64_t>(q.K) / T::kElemsPerByte;
+    CUtensorMap map_w, map_x;
+    if (!umma::make_map_2d_u8(&map_w, q.Bt, row_bytes, static_cast<uint64_t>(q.N), kBM) ||
+        !umma::make_map_2d_u8(&map_x, q.A, row_bytes, static_cast<uint64_t>(q.M), NT))
+        return fail(SPK_CUDA_ERROR, "umma decode gemm: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
+    auto kernel = qgemm_umma_decode_kernel<NT, MODE>;
+    static bool configured[16] = {};
+    if (!configured[dev->device & 15]) {
+        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        configured[dev->device & 15] = true;
+    }
+    DecodeParams p{};
+    p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
+    p.scale_a = q.scale_a, p.scale_b = q.scale_b;
+    p.sfw = sfw, p.sfx = sfx;
+    p.sf_tiles_per_rowblock = MODE == kNvfp4 ? q.K / 64 : q.K / 128;
+    p.n_tiles = cdiv(q.N, kBM);
+    const int k_blocks = cdiv(static_cast<int>(row_bytes), kBKBytes);
+    // one wave of one CTA per SM: as many K slices as fit, at least two K blocks per slice. Two CTAs
+    // per SM (SPK_QDECODE_CTAS_PER_SM=2) measured slower at N = 4096: 9 slices instead of 4 more than
+    // double the partial-sum traffic and the completion tail (fp8 64 x 4096 x 14336: 24.9 us against 19.7).
+    static const int per_sm = [] {
+        const char* e = std::getenv("SPK_QDECODE_CTAS_PER_SM");
+        return e && *e ? std::max(1, std::atoi(e)) : 1;
+    }();
+    p.split = std::max(1, std::min(per_sm * dev->sm_count / p.n_tiles, k_blocks / 2));
+    p.partials = partials, p.counters = dev->counters, p.status = dev->status;
+    kernel<<<p.n_tiles * p.split, 192, Cfg::kSmem, stream>>>(map_w, map_x, p);
+    SPK_CHECK_LAUNCH();
+    return SPK_OK;
+}
+
+template <int MODE>
+int launch_decode_nt(const simt::Params& q, const unsigned char* sfw, const unsigned char* sfx, float* partials,
+                     DeviceState* dev, cudaStream_t stream) {
+    if (q.M <= 16) return launch_decode<16, MODE>(q, sfw, sfx, partials, dev, stream);
+    if (q.M <= 32) return launch_decode<32, MODE>(q, sfw, sfx, partials, dev, stream);
+    return launch_decode<64, MODE>(q, sfw, sfx, partials, dev, stream);
+}
+
+bool decode_fits(const simt::Params& p, size_t scratch_bytes_before) {
+    return static_cast<int64_t>(p.M) * p.N + static_cast<int64_t>(scratch_bytes_before / 4) <= kPartialFloats &&
+           cdiv(p.N, kBM) * 4 <= kCounters;
+}
+
 // Row-major ue8m0 scales [rows][K/32] (the fp8 MX API layout) -> the blocked layout the tensor core
 // reads, rows padded to 128 with zero bytes. One thread per 4 scales (one 32-bit word).
 __global__ void __launch_bounds__(256)
@@ -302,15 +553,22 @@ bool umma_disabled() {
 
 }  // namespace
 
-// Variant 3 (and 2) of fp8gemm: every shape with M > 64 runs on the tensor cores. In MX mode the
+// Variant 3 (and 2) of fp8gemm: every shape with M > 64 runs on the tensor cores as 128 x BN tiles, and
+// variant 3 takes M <= 64 with the weights as the 128-row operand and K split over the SMs. In MX mode the
 // row-major scales are first rewritten into the blocked layout inside the per-device scratch.
 int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t stream, bool* taken) {
     *taken = false;
-    (void)variant;
-    if (p.M <= 64 || !aligned16(p.C) || umma_disabled()) return SPK_OK;
+    if (umma_disabled()) return SPK_OK;
+    const bool decode = p.M <= 64;
+    if (decode ? variant != 3 : !aligned16(p.C)) return SPK_OK;  // variant 2 keeps the reference's tile rule
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;
     if (!mx) {
+        if (decode) {
+            if (!decode_fits(p, 0)) return SPK_OK;
+            *taken = true;
+            return launch_decode_nt<kFp8>(p, nullptr, nullptr, dev->partials, dev, stream);
+        }
         *taken = true;
         return p.N % 256 == 0 ? launch_umma<256, kFp8>(p, nullptr, nullptr, dev, stream)
                               : launch_umma<128, kFp8>(p, nullptr, nullptr, dev, stream);
@@ -318,6 +576,7 @@ int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t s
     const int cols = p.K / 32;
     const size_t a_bytes = static_cast<size_t>(cdiv(p.M, 128)) * 128 * cols, b_bytes = static_cast<size_t>(cdiv(p.N, 128)) * 128 * cols;
     if (a_bytes + b_bytes > static_cast<size_t>(kPartialFloats) * sizeof(float)) return SPK_OK;  // scratch too small
+    if (decode && !decode_fits(p, a_bytes + b_bytes)) return SPK_OK;
     *taken = true;
     unsigned char* sfa = reinterpret_cast<unsigned char*>(dev->partials);
     unsigned char* sfb = sfa + a_bytes;
@@ -325,19 +584,30 @@ int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t s
     mx_scales_to_blocked_kernel<<<static_cast<unsigned>(cdiv64(wa, 256)), 256, 0, stream>>>(p.sfa, sfa, p.M, cols, wa);
     mx_scales_to_blocked_kernel<<<static_cast<unsigned>(cdiv64(wb, 256)), 256, 0, stream>>>(p.sfb, sfb, p.N, cols, wb);
     SPK_CHECK_LAUNCH();
-    const int rc = p.N % 256 == 0 ? launch_umma<256, kFp8Mx>(p, sfa, sfb, dev, stream)
-                                  : launch_umma<128, kFp8Mx>(p, sfa, sfb, dev, stream);
+    int rc;
+    if (decode)  // the split-K partials live behind the repacked scales
+        rc = launch_decode_nt<kFp8Mx>(p, sfb, sfa, dev->partials + (a_bytes + b_bytes) / 4, dev, stream);
+    else
+        rc = p.N % 256 == 0 ? launch_umma<256, kFp8Mx>(p, sfa, sfb, dev, stream) : launch_umma<128, kFp8Mx>(p, sfa, sfb, dev, stream);
     if (rc != SPK_OK) return rc;
     // the scratch is shared with the split-K kernels, which expect it zeroed
     SPK_CUDA(cudaMemsetAsync(sfa, 0, a_bytes + b_bytes, stream));
     return SPK_OK;
 }
 
-// Variant 2 of fp4gemm (M and N multiples of 128 by its rule).
+// Variant 2 of fp4gemm (M and N multiples of 128 by its rule) and the decode route of variant 1 (M <= 64).
 int fp4gemm_umma_try(const simt::Params& p, int format, cudaStream_t stream, bool* taken) {
     *taken = false;
-    if (p.M % 128 != 0 || p.N % 128 != 0 || !aligned16(p.C) || umma_disabled()) return SPK_OK;
+    if (umma_disabled()) return SPK_OK;
     DeviceState* dev = nullptr;
+    if (p.M <= 64) {  // decode: reached through variant 1
+        if (!decode_fits(p, 0)) return SPK_OK;
+        if (int rc = device_state(&dev)) return rc;
+        *taken = true;
+        return format == SPK_FP4_NVFP4 ? launch_decode_nt<kNvfp4>(p, p.sfb, p.sfa, dev->partials, dev, stream)
+                                       : launch_decode_nt<kMxfp4>(p, p.sfb, p.sfa, dev->partials, dev, stream);
+    }
+    if (p.M % 128 != 0 || p.N % 128 != 0 || !aligned16(p.C)) return SPK_OK;
     if (int rc = device_state(&dev)) return rc;
     *taken = true;
     if (format == SPK_FP4_NVFP4)

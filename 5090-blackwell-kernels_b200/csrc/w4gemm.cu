@@ -636,6 +636,9 @@ int launch_stream(const StreamParams& p, bool whole, const DeviceState& dev, cud
 }  // namespace spk
 
 namespace spk {
+// defined in w4gemm_tmem.cu
+int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
+                    int K, cudaStream_t stream, bool* taken);
 // defined in w4gemm_umma.cu
 int w4gemm_umma_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
                     int K, cudaStream_t stream, bool* taken);
@@ -679,6 +682,8 @@ extern "C" int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void*
     }
     if (variant == 2) {  // the tensor-core route for mid-size token counts
         bool taken = false;
+        const int rc0 = w4gemm_tmem_try(A, packed, scales, zeros, C, M, N, K, stream, &taken);
+        if (taken || rc0 != SPK_OK) return rc0;
         const int rc = w4gemm_umma_try(A, packed, scales, zeros, C, M, N, K, stream, &taken);
         if (taken || rc != SPK_OK) return rc;
     }

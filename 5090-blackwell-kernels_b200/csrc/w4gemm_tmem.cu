@@ -1,0 +1,492 @@
+// W4A16 GEMM on the tcgen05 tensor cores with the dequantized weights held in TENSOR MEMORY
+// (operand A of tcgen05.mma read from TMEM), for M <= 64.
+//
+//   D[n][token] (TMEM, 128 x NT fp32)  +=  W^T[n][k] (TMEM, bf16)  *  A[token][k] (smem, bf16, K-major)
+//
+// Compared with staging the dequantized weights in shared memory this drops the 16-byte shared
+// stores, their bank traffic and the generic->async proxy fence from the dequant warps (a
+// tcgen05.st plus tcgen05.wait::st takes their place), and it frees 96 KiB of shared memory, which
+// goes into deeper code rings. TMEM also holds six 128-k groups of weights instead of three, so a
+// dequant warp can take a whole 2-group chunk (one 2 KiB bulk copy, one barrier wait, one hand-off)
+// per iteration.
+//
+// A dequant lane (g, c) of the packed layout holds, for columns g and g + 8 of its strip, the k
+// quads 8c + 4(r & 1) + 32(r >> 1) + {0..3}, r = 0..3, of a 64-k unit. tcgen05.st.16x256b places
+// lane (g, c)'s registers at rows g / g + 8 and 32-bit columns 2c, 2c + 1 of each 8-column block,
+// i.e. block r (one K = 16 MMA step) position 4c + i holds k = 8c + 4(r & 1) + 32(r >> 1) + i.
+// The activation tile is therefore written with the same order: the producers copy the token
+// rows in 8-byte pieces (cp.async) to the permuted position, in the 128-byte-swizzled K-major
+// layout, and the tensor core contracts position against position.
+//
+// One persistent CTA per SM owns a contiguous range of (128-column super-strip, 2-group chunk)
+// units. Roles (23 warps):
+//   warps 0-15  dequant: strip 2 (w % 4) + (w / 4) % 2 (its 16 TMEM lanes lie in the lane quarter
+//               w % 4 that the warp may access), chunks of parity w / 8 of the CTA's sequence
+//   warps 16-19 epilogue (TMEM lane quarter w % 4)
+//   warp 20     MMA: loop warp-wide, one elected lane issues 16 tcgen05.mma per chunk
+//   warps 21-22 activation producers (unit w % 2 of every group)
+// TMEM columns: accumulators at 0 and NT (double buffered), weights at 128 + 128 cs + 64 sub +
+// 32 h + 8 r for chunk stage cs (3), group sub, unit h, MMA step r.
+#include <algorithm>
+
+#include "spk_common.cuh"
+#include "umma_sm100.cuh"
+#include "w4_layout.cuh"
+
+namespace spk {
+namespace {
+
+using ptx::bulk_g2s;
+using ptx::mbar_arrive;
+using ptx::mbar_arrive_expect_tx;
+using ptx::mbar_init;
+using ptx::mbar_wait;
+
+constexpr int kStrips = 8;        // 16-column strips per super-strip
+constexpr int kChunkGroups = 2;   // groups per chunk
+constexpr int kSets = 2;          // dequant warps per strip; set s takes chunks of parity s
+constexpr int DW = kStrips * kSets;
+constexpr int kChunkStages = 3;   // chunks of dequantized weights resident in TMEM
+constexpr int kCodeSlots = 3;     // per-warp ring of one-chunk code pieces
+constexpr int kActStages = 4;     // one group per slot
+constexpr int kActInFlight = 3;   // cp.async groups a producer keeps in flight
+constexpr int kEpilogueWarp0 = DW, kMmaWarp = DW + 4, kProducerWarp0 = DW + 5;
+constexpr int kProducers = 2;     // activation producer warps: unit (w & 1); with 4, rows are split by (w >> 1) too
+constexpr int kThreadsT = (DW + 5 + kProducers) * 32;
+constexpr int kTmemColsT = 512;
+constexpr int kWeightCol0 = 128;  // first TMEM column of the weight stages
+
+struct W4TmemParams {
+    const unsigned char* A;  // activations bf16 [M][K]
+    const unsigned char* packed;
+    const unsigned char* scales;
+    const unsigned char* zeros;
+    __nv_bfloat16* C;
+    int M, N, K, G, super_strips;
+    float* partials;
+    unsigned* counters;
+    int* status;
+};
+
+template <int NT, bool ASYM>
+struct W4TmemSmem {
+    static constexpr int kActBytes = 2 * NT * 128;  // one group: two 64-k units of NT token rows
+    static constexpr int kCodeBytes = kChunkGroups * w4::kGroupBytes;
+    static constexpr int kSlotBytes = kCodeBytes + kChunkGroups * 32 + (ASYM ? kChunkGroups * 16 : 0);
+    static constexpr int kCodeRing = DW * kCodeSlots * kSlotBytes;
+    static constexpr int kCodeArrivals = 1 + 2 * kChunkGroups + (ASYM ? kChunkGroups : 0);
+    static constexpr int kBarriers = 1024;
+    static constexpr int kTotal = 1024 + kActStages * kActBytes + kCodeRing + kBarriers;
+};
+
+__device__ __forceinline__ void cp_async16_t(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8_t(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_t() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_t() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_t(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(ptx::smem_u32(bar)) : "memory");
+}
+
+// 16 TMEM lanes x 32 columns: registers 4r..4r+3 of lane (g, c) go to rows g (first two) and
+// g + 8 (last two), columns 8r + 2c and 8r + 2c + 1.
+__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem], bf16 operands, K = 16.
+__device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+
+template <int NT, bool ASYM>
+__global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const W4TmemParams p) {
+    using L = W4TmemSmem<NT, ASYM>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
+    unsigned char* acts = base;
+    unsigned char* codes = acts + kActStages * L::kActBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(codes + L::kCodeRing);
+    uint64_t* act_full = bars;                    // [AS] one arrive per producer warp
+    uint64_t* act_empty = act_full + kActStages;  // [AS] MMA commit
+    uint64_t* a_ready = act_empty + kActStages;   // [CS] the 8 dequant warps of the chunk's set
+    uint64_t* a_free = a_ready + kChunkStages;    // [CS] MMA commit
+    uint64_t* acc_ready = a_free + kChunkStages;  // [2] MMA commit
+    uint64_t* acc_free = acc_ready + 2;           // [2] 4 epilogue warps
+    uint64_t* code_bar = acc_free + 2;            // [DW][kCodeSlots]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(code_bar + DW * kCodeSlots);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = p.G / kChunkGroups;  // chunks per super-strip
+    const long long total = static_cast<long long>(p.super_strips) * chunks;
+    const int f0 = static_cast<int>(blockIdx.x * total / gridDim.x);
+    const int f1 = static_cast<int>((blockIdx.x + 1) * total / gridDim.x);
+    const int n_chunks = f1 - f0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kActStages; ++s) {
+            mbar_init(&act_full[s], kProducers);
+            mbar_init(&act_empty[s], 1);
+        }
+        for (int s = 0; s < kChunkStages; ++s) {
+            mbar_init(&a_ready[s], kStrips);
+            mbar_init(&a_free[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_ready[b], 1);
+            mbar_init(&acc_free[b], 4);
+        }
+        for (int i = 0; i < DW * kCodeSlots; ++i) mbar_init(&code_bar[i], L::kCodeArrivals);
+        ptx::fence_mbar_init();
+    }
+    if (warp == kMmaWarp) umma::tmem_alloc(tmem_slot, kTmemColsT);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DW) {
+        // ================= dequant warps =================
+        const int gl = lane >> 2;
+        const int strip = 2 * (warp & 3) + ((warp >> 2) & 1), set = warp >> 3;
+        const uint32_t my_tmem = tmem_base + (static_cast<uint32_t>(16 * strip) << 16) + kWeightCol0;
+        unsigned char* ring = codes + warp * (kCodeSlots * L::kSlotBytes);
+        uint64_t* my_bar = code_bar + warp * kCodeSlots;
+        // next chunk to fetch: this warp takes chunks f0 + set, f0 + set + 2, ...
+        int pf = f0 + set, p_slot = 0, p_ss = pf / chunks, p_ch = pf - p_ss * chunks;
+        auto issue = [&]() {
+            if (pf >= f1) return;
+            const int t = p_ss * kStrips + strip, g0 = p_ch * kChunkGroups;
+            unsigned char* slot = ring + p_slot * L::kSlotBytes;
+            uint64_t* bar = &my_bar[p_slot];
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, L::kCodeBytes);
+                bulk_g2s(slot, p.packed + (static_cast<size_t>(t) * p.G + g0) * w4::kGroupBytes, L::kCodeBytes, bar);
+            } else if (lane <= 2 * kChunkGroups) {
+                const int j = lane - 1;  // scale row j / 2 of the chunk, 16-byte half j % 2
+                cp_async16_t(slot + L::kCodeBytes + j * 16,
+                             p.scales + (static_cast<size_t>(g0 + (j >> 1)) * p.N + 16 * t) * 2 + (j & 1) * 16);
+                cp_async_arrive_t(bar);
+            } else if (ASYM && lane <= 3 * kChunkGroups) {
+                const int j = lane - 1 - 2 * kChunkGroups;
+                cp_async16_t(slot + L::kCodeBytes + kChunkGroups * 32 + j * 16, p.zeros + static_cast<size_t>(g0 + j) * p.N + 16 * t);
+                cp_async_arrive_t(bar);
+            }
+            pf += kSets;
+            p_ch += kSets;
+            while (p_ch >= chunks) p_ch -= chunks, ++p_ss;
+            p_slot = p_slot + 1 == kCodeSlots ? 0 : p_slot + 1;
+        };
+        for (int i = 0; i < kCodeSlots; ++i) issue();
+
+        const int n_mine = n_chunks > set ? (n_chunks - set + 1) / 2 : 0;
+        int slot_i = 0, cs = set;  // chunk stage of local chunk index set, set + 2, ...
+        unsigned code_ph = 0, ph = 0;
+        bool ok = true;
+        for (int it = 0; it < n_mine && ok; ++it) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&my_bar[slot_i], code_ph, p.status));
+            if (!ok) break;
+            const unsigned char* slot = ring + slot_i * L::kSlotBytes;
+            const uint4* cw = reinterpret_cast<const uint4*>(slot);
+#pragma unroll
+            for (int sub = 0; sub < kChunkGroups; ++sub) {
+                const unsigned short* sc = reinterpret_cast<const unsigned short*>(slot + L::kCodeBytes + sub * 32);
+                const uint32_t s_lo = w4::splat16(sc[gl]), s_hi = w4::splat16(sc[gl + 8]);
+                uint32_t o_lo = w4::kSymOffset, o_hi = w4::kSymOffset;
+                if (ASYM) {
+                    const unsigned char* zp = slot + L::kCodeBytes + kChunkGroups * 32 + sub * 16;
+                    o_lo = w4::offset_pair(zp[gl]);
+                    o_hi = w4::offset_pair(zp[gl + 8]);
+                }
+                uint32_t x[2][4][4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 q = cw[(sub * 2 + h) * 32 + lane];
+                    w4::dequant_word(q.x, o_lo, o_hi, s_lo, s_hi, x[h][0]);
+                    w4::dequant_word(q.y, o_lo, o_hi, s_lo, s_hi, x[h][1]);
+                    w4::dequant_word(q.z, o_lo, o_hi, s_lo, s_hi, x[h][2]);
+                    w4::dequant_word(q.w, o_lo, o_hi, s_lo, s_hi, x[h][3]);
+                }
+                if (sub == 0) {  // the stage is free once the MMAs of three chunks ago have read it
+                    ok = __all_sync(0xffffffffu, mbar_wait(&a_free[cs], ph ^ 1u, p.status));
+                    if (!ok) break;
+                    umma::fence_after_sync();
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t v[16];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        v[4 * r + 0] = x[h][r][0];
+                        v[4 * r + 1] = x[h][r][2];
+                        v[4 * r + 2] = x[h][r][1];
+                        v[4 * r + 3] = x[h][r][3];
+                    }
+                    tmem_st_16x256b_x4(my_tmem + cs * 128 + sub * 64 + h * 32, v);
+                }
+            }
+            if (!ok) break;
+            __syncwarp();
+            issue();
+            if (++slot_i == kCodeSlots) slot_i = 0, code_ph ^= 1u;
+            tmem_st_wait();
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_ready[cs]);
+            cs += kSets;
+            if (cs >= kChunkStages) cs -= kChunkStages, ph ^= 1u;
+        }
+    } else if (warp >= kProducerWarp0) {
+        // ================= activation producers: unit h of every group, 8-byte pieces permuted =================
+        const int h = (warp - kProducerWarp0) & 1;
+        const int sp = lane & 15;                              // source piece of the 128-byte unit row
+        constexpr int kRowStep = kProducers;                   // rows a warp covers per pass: 2 per lane half x warps per unit
+        const int t0 = 2 * ((warp - kProducerWarp0) >> 1) + (lane >> 4);  // this lane's rows: t0, t0 + kRowStep, ...
+        const int r = ((sp >> 3) << 1) | (sp & 1), c = (sp >> 1) & 3;
+        const int dp = 4 * r + c;                              // destination piece
+        const uint32_t acts_u32 = ptx::smem_u32(acts) + h * (NT * 128) + (dp & 1) * 8;
+        uint32_t sw[8 / kRowStep];                             // row offset + swizzled chunk of rows t0 + kRowStep j (< 8)
+#pragma unroll
+        for (int j = 0; j < 8 / kRowStep; ++j) {
+            const int t = t0 + kRowStep * j;
+            sw[j] = t * 128 + (((dp >> 1) ^ t) << 4);
+        }
+        const unsigned char* src_lane = p.A + h * 128 + sp * 8;
+        const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+        const int n_groups = n_chunks * kChunkGroups;
+        int s = 0, sig = 0, sig_s = 0, ch = f0 % chunks, sub = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int gi = 0; gi < n_groups && ok; ++gi) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&act_empty[s], ph ^ 1u, p.status));
+            if (!ok) break;
+            const unsigned char* src = src_lane + static_cast<size_t>(ch * kChunkGroups + sub) * 256;
+            const uint32_t dst = acts_u32 + s * L::kActBytes;
+            for (int t = t0; t < p.M; t += 8) {  // rows t + kRowStep j differ only in the swizzle term
+#pragma unroll
+                for (int j = 0; j < 8 / kRowStep; ++j)
+                    if (t + kRowStep * j < p.M) cp_async8_t(dst + (t - t0) * 128 + sw[j], src + (t + kRowStep * j) * row_bytes);
+            }
+            cp_async_commit_t();
+            if (gi - sig >= kActInFlight - 1) {
+                cp_async_wait_t<kActInFlight - 1>();
+                ptx::fence_proxy_async();  // cp.async wrote through the generic proxy; the tensor core reads through the async one
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&act_full[sig_s]);
+                ++sig;
+                if (++sig_s == kActStages) sig_s = 0;
+            }
+            if (++s == kActStages) s = 0, ph ^= 1u;
+            if (++sub == kChunkGroups) {
+                sub = 0;
+                if (++ch == chunks) ch = 0;
+            }
+        }
+        cp_async_wait_t<0>();
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (ok)
+            for (; sig < n_groups; ++sig) {
+                if (lane == 0) mbar_arrive(&act_full[sig_s]);
+                if (++sig_s == kActStages) sig_s = 0;
+            }
+    } else if (warp == kMmaWarp) {
+        // ================= MMA issuer: the loop runs warp-wide, one elected lane issues =================
+        constexpr uint32_t idesc = umma::instr_desc(128, NT, 1, 1);  // bf16 x bf16 -> f32
+        const uint64_t bdesc0 = umma::smem_desc_k128(acts);
+        int seg = 0, cs = 0, as = 0, ch = f0 % chunks;
+        unsigned ph = 0, aph = 0;
+        bool ok = true, fresh = true;
+        for (int f = f0; f < f1 && ok; ++f) {
+            const int buf = seg & 1;
+            if (fresh) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&acc_free[buf], ((seg >> 1) & 1) ^ 1, p.status));
+                if (!ok) break;
+            }
+            const uint32_t acc = tmem_base + buf * NT;
+            ok = __all_sync(0xffffffffu, mbar_wait(&a_ready[cs], ph, p.status));
+            if (!ok) break;
+            for (int sub = 0; sub < kChunkGroups && ok; ++sub) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&act_full[as], aph, p.status));
+                if (!ok) break;
+                umma::fence_after_sync();
+                const uint64_t bd = bdesc0 + static_cast<uint64_t>(as) * (L::kActBytes >> 4);
+                const uint32_t wa = tmem_base + kWeightCol0 + cs * 128 + sub * 64;
+                if (umma::elect_one()) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r)
+                            mma_f16_ta(acc, wa + h * 32 + r * 8, bd + h * (NT * 128 >> 4) + 2 * r, idesc,
+                                       !fresh || sub > 0 || h > 0 || r > 0);
+                    umma::mma_commit(&act_empty[as]);
+                }
+                __syncwarp();
+                if (++as == kActStages) as = 0, aph ^= 1u;
+            }
+            if (!ok) break;
+            fresh = false;
+            const bool seg_end = ch == chunks - 1 || f == f1 - 1;
+            if (umma::elect_one()) {
+                umma::mma_commit(&a_free[cs]);
+                if (seg_end) umma::mma_commit(&acc_ready[buf]);
+            }
+            __syncwarp();
+            if (++cs == kChunkStages) cs = 0, ph ^= 1u;
+            if (seg_end) ++seg, fresh = true;
+            if (++ch == chunks) ch = 0;
+        }
+    } else {
+        // ================= epilogue warps: TMEM lane quarter = warp % 4 =================
+        const int quarter = warp & 3;
+        int pend_ss[2] = {0, 0}, pend_n[2] = {0, 0}, n_pend = 0;
+        int seg = 0, seg_ch0 = f0 % chunks;
+        bool ok = true;
+        for (int f = f0; f < f1 && ok; ++f) {
+            const int ss = f / chunks, ch = f - ss * chunks;
+            if (!(ch == chunks - 1 || f == f1 - 1)) continue;
+            const int buf = seg & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(&acc_ready[buf], (seg >> 1) & 1, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
+            uint32_t v[NT];
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                uint32_t r[16];
+                umma::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * NT + c0, r);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[c0 + i] = r[i];
+            }
+            umma::tmem_ld_wait();
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_free[buf]);
+            const int n = ss * 128 + quarter * 32 + lane;  // TMEM lane = column of the super-strip
+            const bool whole_k = seg_ch0 == 0 && ch == chunks - 1;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                if (t < p.M) {
+                    if (whole_k)
+                        p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[t]));
+                    else
+                        atomicAdd(p.partials + static_cast<size_t>(t) * p.N + n, __uint_as_float(v[t]));
+                }
+            }
+            if (!whole_k) {
+                pend_ss[n_pend] = ss;
+                pend_n[n_pend] = ch - seg_ch0 + 1;
+                ++n_pend;
+            }
+            ++seg;
+            seg_ch0 = 0;
+        }
+        // completion of the partial segments: one fence, then the per-(tile, quarter) counters
+        if (n_pend > 0) {
+            __threadfence();
+            __syncwarp();
+            for (int i = 0; i < n_pend; ++i) {
+                unsigned done = 0;
+                unsigned* counter = p.counters + pend_ss[i] * 4 + quarter;
+                if (lane == 0) done = atomicAdd(counter, static_cast<unsigned>(pend_n[i]));
+                done = __shfl_sync(0xffffffffu, done, 0);
+                if (done + static_cast<unsigned>(pend_n[i]) == static_cast<unsigned>(chunks)) {
+                    __threadfence();
+                    const int n = pend_ss[i] * 128 + quarter * 32 + lane;
+                    for (int t0 = 0; t0 < p.M; t0 += 16) {  // all loads of a batch in flight together
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[j] = t0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (t0 + j < p.M) {
+                                p.C[static_cast<size_t>(t0 + j) * p.N + n] = __float2bfloat16_rn(v[j]);
+                                __stcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n, 0.f);
+                            }
+                    }
+                    if (lane == 0) *counter = 0u;
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) umma::tmem_dealloc(tmem_base, kTmemColsT);
+}
+
+template <int NT, bool ASYM>
+int launch_w4_tmem(W4TmemParams p, DeviceState* dev, cudaStream_t stream) {
+    using L = W4TmemSmem<NT, ASYM>;
+    static_assert(L::kTotal <= 227 * 1024, "w4 tmem kernel exceeds shared memory");
+    static_assert(L::kSlotBytes % 16 == 0 && (NT * 128) % 1024 == 0, "slot alignment");
+    static_assert(2 * NT <= kWeightCol0 && kWeightCol0 + kChunkStages * 128 <= kTmemColsT, "TMEM column budget");
+    auto kernel = w4_tmem_kernel<NT, ASYM>;
+    static bool configured[16] = {};
+    if (!configured[dev->device & 15]) {
+        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+        configured[dev->device & 15] = true;
+    }
+    p.super_strips = p.N / 128;
+    const long long total = static_cast<long long>(p.super_strips) * (p.G / kChunkGroups);
+    const int grid = static_cast<int>(std::min<long long>(dev->sm_count, total));
+    kernel<<<grid, kThreadsT, L::kTotal, stream>>>(p);
+    SPK_CHECK_LAUNCH();
+    return SPK_OK;
+}
+
+}  // namespace
+
+// Takes min_m <= M <= 64 with N a multiple of 128, an even number of groups and 16-byte-aligned
+// activation rows; `taken` says whether it ran. Off unless SPK_W4_TMEM=1 (SPK_W4_TMEM_MIN_M moves
+// the lower bound, default 1).
+int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
+                    int K, cudaStream_t stream, bool* taken) {
+    *taken = false;
+    static const int enabled = [] {
+        const char* e = std::getenv("SPK_W4_TMEM");
+        return e && *e ? std::atoi(e) : 0;
+    }();
+    static const int min_m = [] {
+        const char* e = std::getenv("SPK_W4_TMEM_MIN_M");
+        return e && *e ? std::atoi(e) : 1;
+    }();
+    if (!enabled || M < min_m || M > 64 || N % 128 != 0 || (K / w4::kGroup) % kChunkGroups != 0) return SPK_OK;
+    if (static_cast<int64_t>(M) * N > kPartialFloats || (N / 128) * 4 > kCounters) return SPK_OK;
+    if (reinterpret_cast<uintptr_t>(A) % 16 != 0) return SPK_OK;
+    DeviceState* dev = nullptr;
+    if (int rc = device_state(&dev)) return rc;
+    W4TmemParams p{};
+    p.A = static_cast<const unsigned char*>(A);
+    p.packed = reinterpret_cast<const unsigned char*>(packed);
+    p.scales = static_cast<const unsigned char*>(scales);
+    p.zeros = zeros;
+    p.C = static_cast<__nv_bfloat16*>(C);
+    p.M = M, p.N = N, p.K = K, p.G = K / w4::kGroup;
+    p.partials = dev->partials, p.counters = dev->counters, p.status = dev->status;
+    *taken = true;
+    const int nt = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+    if (zeros)
+        return nt == 16 ? launch_w4_tmem<16, true>(p, dev, stream)
+               : nt == 32 ? launch_w4_tmem<32, true>(p, dev, stream)
+                          : launch_w4_tmem<64, true>(p, dev, stream);
+    return nt == 16 ? launch_w4_tmem<16, false>(p, dev, stream)
+           : nt == 32 ? launch_w4_tmem<32, false>(p, dev, stream)
+                      : launch_w4_tmem<64, false>(p, dev, stream);
+}
+
+}  // namespace spk

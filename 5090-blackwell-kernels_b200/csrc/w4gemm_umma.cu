@@ -55,6 +55,9 @@ constexpr int kProducerWarp = DW, kMmaWarp = DW + 1, kEpilogueWarp0 = DW + 2;
 constexpr int kUnitBytes = 128 * 128;          // 128 columns x 64 k of bf16
 constexpr int kOperandStage = 2 * kUnitBytes;  // one group
 constexpr int kThreadsU = (DW + 6) * 32;
+// arrivals that complete a code slot: the lane that posts the bulk copy, and one per cp.async lane
+template <bool ASYM>
+constexpr int kCodeArrivals = 1 + 2 + (ASYM ? 1 : 0);
 
 struct W4UmmaParams {
     const unsigned char* packed;
@@ -104,7 +107,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap map_act, const W4UmmaParams p
     uint64_t* a_free = a_ready + kStagesU;     // [S] MMA commit
     uint64_t* acc_ready = a_free + kStagesU;   // [2] MMA commit
     uint64_t* acc_free = acc_ready + 2;        // [2] 4 epilogue warps
-    uint64_t* code_bar = acc_free + 2;         // [DW][kCodeSlots] 1 expect_tx arrive + 32 cp.async arrives
+    uint64_t* code_bar = acc_free + 2;         // [DW][kCodeSlots] 1 expect_tx arrive + the cp.async lanes' arrives
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(code_bar + DW * kCodeSlots);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,7 +130,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap map_act, const W4UmmaParams p
             mbar_init(&acc_ready[b], 1);
             mbar_init(&acc_free[b], 4);
         }
-        for (int i = 0; i < DW * kCodeSlots; ++i) mbar_init(&code_bar[i], 33);
+        for (int i = 0; i < DW * kCodeSlots; ++i) mbar_init(&code_bar[i], kCodeArrivals<ASYM>);
         ptx::fence_mbar_init();
         umma::prefetch_tensormap(&map_act);
     }
@@ -156,10 +159,11 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap map_act, const W4UmmaParams p
             } else if (lane < 3) {
                 cp_async16_u(slot + L::kCodeBytes + (lane - 1) * 16,
                              p.scales + (static_cast<size_t>(g) * p.N + 16 * t) * 2 + (lane - 1) * 16);
+                cp_async_arrive_u(bar);
             } else if (ASYM && lane == 3) {
                 cp_async16_u(slot + L::kCodeBytes + 32, p.zeros + static_cast<size_t>(g) * p.N + 16 * t);
+                cp_async_arrive_u(bar);
             }
-            cp_async_arrive_u(bar);
             ++pf;
             if (++p_ch == chunks) p_ch = 0, ++p_ss;
             p_slot = p_slot + 1 == kCodeSlots ? 0 : p_slot + 1;

@@ -413,33 +413,65 @@ def run_one_gemm(args) -> None:
     else:
         M, N, K = d0, d1, d2
         a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
-        b = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+        # decode shapes stream the weights: rotate over enough copies to exceed L2 (126 MB)
+        copies = 1 if M > 64 else max(2, -(-(300 << 20) // (N * K)))
+        bs = [torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(copies)]
         if args.kind == "fp8":
-            (qa, sa), (qb, sb) = sk.fp8_quantize(a, "tensor"), sk.fp8_quantize(b, "tensor")
-            calls = [lambda: sk.fp8gemm(qa, qb, sa, sb)]
+            qa, sa = sk.fp8_quantize(a, "tensor")
+            qs = [sk.fp8_quantize(b, "tensor") for b in bs]
+            calls = [lambda q=q: sk.fp8gemm(qa, q[0], sa, q[1]) for q in qs]
         elif args.kind == "mxfp8":
-            (qa, sfa), (qb, sfb) = sk.fp8_quantize(a, "mx"), sk.fp8_quantize(b, "mx")
-            calls = [lambda: sk.fp8gemm(qa, qb, sfa=sfa, sfb=sfb)]
+            qa, sfa = sk.fp8_quantize(a, "mx")
+            qs = [sk.fp8_quantize(b, "mx") for b in bs]
+            calls = [lambda q=q: sk.fp8gemm(qa, q[0], sfa=sfa, sfb=q[1]) for q in qs]
         else:
             qa, sfa, sa = sk.fp4_quantize(a, args.kind)
-            qb, sfb, sb = sk.fp4_quantize(b, args.kind)
-            kw = {} if args.kind == "mxfp4" else {"scale_a": sa.reshape(1), "scale_b": sb.reshape(1)}
-            calls = [lambda: sk.fp4gemm(qa, qb, sfa, sfb, fmt=args.kind, **kw)]
+            qs = [sk.fp4_quantize(b, args.kind) for b in bs]
+            if args.kind == "mxfp4":
+                calls = [lambda q=q: sk.fp4gemm(qa, q[0], sfa, q[1], fmt="mxfp4") for q in qs]
+            else:
+                calls = [lambda q=q: sk.fp4gemm(qa, q[0], sfa, q[1], fmt="nvfp4", scale_a=sa.reshape(1), scale_b=q[2].reshape(1))
+                         for q in qs]
+        del bs
         work, unit = 2 * M * N * K, "TFLOP/s"
+        # the reference's traffic model (scripts/shape_utils.py:342-345): operands + block scales + bf16 output
+        per_elem = {"fp8": 1.0, "mxfp8": 1.0 + 1 / 32, "nvfp4": 0.5 + 1 / 16, "mxfp4": 0.5 + 1 / 32}[args.kind]
+        stream_bytes = (M * K + K * N) * per_elem + 2 * M * N
     for i in range(3):
         calls[i % len(calls)]()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n = max(1, args.steps)
+    timing = "eager launches, CUDA events"
+    if args.graph:
+        # the launches of one pass captured in a CUDA graph: what a decode engine replays
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(len(calls)):
+                calls[i]()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n):
+                calls[i % len(calls)]()
+        graph.replay()
+        torch.cuda.synchronize()
+        timing = "CUDA graph of the launches, CUDA events"
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(n):
-        calls[i % len(calls)]()
+    if args.graph:
+        graph.replay()
+    else:
+        for i in range(n):
+            calls[i % len(calls)]()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / n
     rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    extra = {} if args.kind == "w4" else {"gbps": round(stream_bytes / (ms * 1e-3) / 1e9, 1)}
     print(json.dumps({"one_gemm": [d0, d1, d2], "kind": args.kind, "launches": 3 + n, "us_per_launch": round(ms * 1e3, 2),
-                      "rate": round(rate, 1), "unit": unit, "timing": "eager launches, CUDA events",
+                      "rate": round(rate, 1), "unit": unit, **extra, "timing": timing,
                       "status": sk._C.device_status()}))
 
 
@@ -454,6 +486,7 @@ def main() -> None:
                     help="profiling helper: run --steps launches of one GEMM shape through the public op and exit")
     ap.add_argument("--kind", default="w4", choices=["w4", "fp8", "mxfp8", "nvfp4", "mxfp4"],
                     help="with --one-gemm: which GEMM (w4 takes K,N,M; the others M,N,K)")
+    ap.add_argument("--graph", action="store_true", help="with --one-gemm: time the launches inside one CUDA graph")
     args = ap.parse_args()
     if args.one_gemm:
         run_one_gemm(args)
