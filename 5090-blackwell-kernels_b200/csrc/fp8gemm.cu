@@ -13,6 +13,7 @@
 namespace spk {
 // defined in fp8gemm_umma.cu
 int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t stream, bool* taken);
+int fp8gemm_block128_umma_try(const simt::Params& p, cudaStream_t stream, bool* taken);
 namespace {
 
 int g_v3_route = -1;  // SPK_FP8GEMM_V3_ROUTE_DEFAULT
@@ -121,6 +122,9 @@ extern "C" int spk_fp8gemm_block128(const void* A, const void* Bt, void* C, int 
     p.C = static_cast<__nv_bfloat16*>(C);
     p.M = M, p.N = N, p.K = K;
     p.blk_a = sA, p.blk_b = sB;
+    bool taken = false;
+    const int rc = fp8gemm_block128_umma_try(p, static_cast<cudaStream_t>(stream), &taken);
+    if (taken || rc != SPK_OK) return rc;
     return simt::launch<simt::kFp8Block128>(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -533,6 +533,159 @@ bool decode_fits(const simt::Params& p, size_t scratch_bytes_before) {
            cdiv(p.N, kBM) * 4 <= kCounters;
 }
 
+// ---- fp8 with fp32 block scales (1 x 128 of A, 128 x 128 of Bt) ------------------------------------
+//
+// The tensor core has no fp32 block scaling, so every 128-k block is contracted on its own into a
+// TMEM buffer (4 MMAs of K = 32, the first one overwriting) and the epilogue warps fold it into fp32
+// register accumulators with the block's two scales: acc += (sA[m][kb] * sB[n / 128][kb]) * block.
+// Two TMEM buffers let the folding of block kb overlap the MMAs of block kb + 1. One CTA per
+// 128 x 128 tile (one sB per block and tile); a thread owns one row and its 128 accumulators.
+struct Block128Params {
+    __nv_bfloat16* C;
+    int M, N, K;
+    const float* sA;  // [M][K / 128]
+    const float* sB;  // [cdiv(N, 128)][K / 128]
+    int* status;
+};
+
+constexpr int kBlkStages = 4, kBlkBN = 128;
+constexpr int kBlkStageBytes = (kBM + kBlkBN) * kBKBytes;
+constexpr int kBlkSmem = kBlkStages * kBlkStageBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(192, 1)
+qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           const Block128Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kBlkStages * kBlkStageBytes);
+    uint64_t* empty = full + kBlkStages;
+    uint64_t* tfull = empty + kBlkStages;  // [2] MMA commit: a block's sum is complete in TMEM buffer b
+    uint64_t* tfree = tfull + 2;           // [2] the 4 epilogue warps have read buffer b
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfree + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tile_m = blockIdx.x % tiles_m, tile_n = blockIdx.x / tiles_m;
+    const int KB = p.K / 128;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBlkStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tfree[b], 4);
+        }
+        ptx::fence_mbar_init();
+        umma::prefetch_tensormap(&map_a);
+        umma::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) umma::tmem_alloc(tmem_slot, 2 * kBlkBN);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    if (warp == 0) {
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, p.status));
+            if (!ok) break;
+            if (umma::elect_one()) {
+                mbar_arrive_expect_tx(&full[s], kBlkStageBytes);
+                unsigned char* st = tiles + s * kBlkStageBytes;
+                umma::tma_load_2d(st, &map_a, kb * kBKBytes, tile_m * kBM, &full[s]);
+                umma::tma_load_2d(st + kBM * kBKBytes, &map_b, kb * kBKBytes, tile_n * kBlkBN, &full[s]);
+            }
+            __syncwarp();
+            if (++s == kBlkStages) s = 0, ph ^= 1u;
+        }
+    } else if (warp == 1) {
+        constexpr uint32_t idesc = umma::instr_desc(kBM, kBlkBN, 0, 0);  // e4m3 x e4m3 -> f32
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+            const int buf = kb & 1;
+            ok = __all_sync(0xffffffffu,
+                            mbar_wait(&full[s], ph, p.status) && mbar_wait(&tfree[buf], ((kb >> 1) & 1) ^ 1, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
+            if (umma::elect_one()) {
+                const unsigned char* st = tiles + s * kBlkStageBytes;
+                const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + kBM * kBKBytes);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma::mma_f8f6f4(tmem_acc + buf * kBlkBN, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k),
+                                     idesc, k > 0);
+                umma::mma_commit(&empty[s]);
+                umma::mma_commit(&tfull[buf]);
+            }
+            __syncwarp();
+            if (++s == kBlkStages) s = 0, ph ^= 1u;
+        }
+    } else {
+        // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1; a thread owns one row ----
+        const int quarter = warp & 3;
+        const int row = tile_m * kBM + quarter * 32 + lane;
+        const float* sa_row = p.sA + static_cast<size_t>(row < p.M ? row : 0) * KB;
+        const float* sb_row = p.sB + static_cast<size_t>(tile_n) * KB;
+        float acc[kBlkBN];
+#pragma unroll
+        for (int i = 0; i < kBlkBN; ++i) acc[i] = 0.f;
+        bool ok = true;
+        float f_next = KB > 0 ? __ldg(sa_row) * __ldg(sb_row) : 0.f;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+            const int buf = kb & 1;
+            const float f = f_next;
+            if (kb + 1 < KB) f_next = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&tfull[buf], (kb >> 1) & 1, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
+            const uint32_t t0 = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlkBN;
+#pragma unroll
+            for (int c0 = 0; c0 < kBlkBN; c0 += 64) {
+                uint32_t r0[32], r1[32];
+                umma::tmem_ld_32x32(t0 + c0, r0);
+                umma::tmem_ld_32x32(t0 + c0 + 32, r1);
+                umma::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    acc[c0 + i] = fmaf(__uint_as_float(r0[i]), f, acc[c0 + i]);
+                    acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), f, acc[c0 + 32 + i]);
+                }
+            }
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tfree[buf]);
+        }
+        if (ok && row < p.M) {
+#pragma unroll
+            for (int c0 = 0; c0 < kBlkBN; c0 += 32) {
+                const int col = tile_n * kBlkBN + c0;
+                if (col < p.N) {  // N % 64 == 0: a 32-column run is all in or all out
+                    uint4 out[4];
+                    uint32_t* o = reinterpret_cast<uint32_t*>(out);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const __nv_bfloat162 v = __floats2bfloat162_rn(acc[c0 + 2 * j], acc[c0 + 2 * j + 1]);
+                        o[j] = *reinterpret_cast<const uint32_t*>(&v);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(p.C + static_cast<size_t>(row) * p.N + col);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = out[j];
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) umma::tmem_dealloc(tmem_acc, 2 * kBlkBN);
+}
+
 // Row-major ue8m0 scales [rows][K/32] (the fp8 MX API layout) -> the blocked layout the tensor core
 // reads, rows padded to 128 with zero bytes. One thread per 4 scales (one 32-bit word).
 __global__ void __launch_bounds__(256)
@@ -615,6 +768,31 @@ int fp4gemm_umma_try(const simt::Params& p, int format, cudaStream_t stream, boo
                               : launch_umma<128, kNvfp4>(p, p.sfa, p.sfb, dev, stream);
     return p.N % 256 == 0 ? launch_umma<256, kMxfp4>(p, p.sfa, p.sfb, dev, stream)
                           : launch_umma<128, kMxfp4>(p, p.sfa, p.sfb, dev, stream);
+}
+
+// The fp32-block-scaled fp8 GEMM on the tensor cores (every shape; C rows must be 16-byte aligned).
+int fp8gemm_block128_umma_try(const simt::Params& q, cudaStream_t stream, bool* taken) {
+    *taken = false;
+    if (umma_disabled() || !aligned16(q.C)) return SPK_OK;
+    DeviceState* dev = nullptr;
+    if (int rc = device_state(&dev)) return rc;
+    CUtensorMap map_a, map_b;
+    if (!umma::make_map_2d_u8(&map_a, q.A, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M), kBM) ||
+        !umma::make_map_2d_u8(&map_b, q.Bt, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), kBlkBN))
+        return fail(SPK_CUDA_ERROR, "fp8gemm_block128: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
+    static bool configured[16] = {};
+    if (!configured[dev->device & 15]) {
+        SPK_CUDA(cudaFuncSetAttribute(qgemm_umma_block128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBlkSmem));
+        configured[dev->device & 15] = true;
+    }
+    *taken = true;
+    Block128Params p{};
+    p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
+    p.sA = q.blk_a, p.sB = q.blk_b;
+    p.status = dev->status;
+    qgemm_umma_block128_kernel<<<cdiv(q.M, kBM) * cdiv(q.N, kBlkBN), 192, kBlkSmem, stream>>>(map_a, map_b, p);
+    SPK_CHECK_LAUNCH();
+    return SPK_OK;
 }
 
 }  // namespace spk

@@ -393,7 +393,7 @@ def run_ours(args) -> None:
 def run_one_gemm(args) -> None:
     """A small case for ncu and for the secondary GEMMs: one shape through the public op, a few
     launches, timed with CUDA events. w4: K,N,M over 4 weight copies (larger than L2 together for the
-    Llama shapes). fp8 / mxfp8 / nvfp4 / mxfp4: M,N,K of a square-ish compute-bound GEMM."""
+    Llama shapes). fp8 / fp8block / mxfp8 / nvfp4 / mxfp4: M,N,K (weights rotated past L2 when M <= 64)."""
     import torch
 
     import spark_kernels as sk
@@ -420,6 +420,10 @@ def run_one_gemm(args) -> None:
             qa, sa = sk.fp8_quantize(a, "tensor")
             qs = [sk.fp8_quantize(b, "tensor") for b in bs]
             calls = [lambda q=q: sk.fp8gemm(qa, q[0], sa, q[1]) for q in qs]
+        elif args.kind == "fp8block":  # fp32 scales: 1 x 128 blocks of A, 128 x 128 blocks of B
+            qa, sa = sk.fp8_quantize_block128(a.float(), 1)
+            qs = [sk.fp8_quantize_block128(b.float(), 128) for b in bs]
+            calls = [lambda q=q: sk.fp8gemm_block128(qa, q[0], sa, q[1]) for q in qs]
         elif args.kind == "mxfp8":
             qa, sfa = sk.fp8_quantize(a, "mx")
             qs = [sk.fp8_quantize(b, "mx") for b in bs]
@@ -435,7 +439,7 @@ def run_one_gemm(args) -> None:
         del bs
         work, unit = 2 * M * N * K, "TFLOP/s"
         # the reference's traffic model (scripts/shape_utils.py:342-345): operands + block scales + bf16 output
-        per_elem = {"fp8": 1.0, "mxfp8": 1.0 + 1 / 32, "nvfp4": 0.5 + 1 / 16, "mxfp4": 0.5 + 1 / 32}[args.kind]
+        per_elem = {"fp8": 1.0, "fp8block": 1.0, "mxfp8": 1.0 + 1 / 32, "nvfp4": 0.5 + 1 / 16, "mxfp4": 0.5 + 1 / 32}[args.kind]
         stream_bytes = (M * K + K * N) * per_elem + 2 * M * N
     for i in range(3):
         calls[i % len(calls)]()
@@ -484,7 +488,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--one-gemm", default="", metavar="A,B,C",
                     help="profiling helper: run --steps launches of one GEMM shape through the public op and exit")
-    ap.add_argument("--kind", default="w4", choices=["w4", "fp8", "mxfp8", "nvfp4", "mxfp4"],
+    ap.add_argument("--kind", default="w4", choices=["w4", "fp8", "fp8block", "mxfp8", "nvfp4", "mxfp4"],
                     help="with --one-gemm: which GEMM (w4 takes K,N,M; the others M,N,K)")
     ap.add_argument("--graph", action="store_true", help="with --one-gemm: time the launches inside one CUDA graph")
     args = ap.parse_args()
