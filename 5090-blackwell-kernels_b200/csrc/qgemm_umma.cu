@@ -23,6 +23,10 @@
 #include "qgemm_simt.cuh"
 #include "umma_sm100.cuh"
 
+#ifndef UMMA_FP8_TWO_CTAS
+#define UMMA_FP8_TWO_CTAS 1
+#endif
+
 namespace spk {
 namespace {
 
@@ -33,7 +37,7 @@ using ptx::mbar_wait;
 
 enum UmmaMode { kFp8 = 0, kFp8Mx = 1, kNvfp4 = 2, kMxfp4 = 3 };
 
-constexpr int kBM = 128, kBKBytes = 128, kStages = 4;
+constexpr int kBM = 128, kBKBytes = 128;
 constexpr int kSfTile = 512;             // 128 rows x 4 scale bytes
 constexpr int kSfColsPerStage = 16 + 32;  // TMEM columns kept for one stage's scales (A: <= 16, B: <= 32)
 
@@ -53,6 +57,11 @@ struct UmmaCfg {
     static constexpr int kSfABytes = T::kTiles * kSfTile, kSfBBytes = (BN / 128) * T::kTiles * kSfTile;
     static constexpr int kTxBytes = kABytes + kBBytes + kSfABytes + kSfBBytes;  // what lands per stage
     static constexpr int kStageBytes = (kTxBytes + 1023) / 1024 * 1024;           // stages keep the tile alignment
+    // Per-tensor fp8 runs two CTAs per SM with two stages each: one CTA's epilogue (TMEM -> bf16
+    // stores) and prologue then overlap the other's MMAs. The block-scaled modes need their TMEM
+    // columns for scales and keep one CTA per SM with four stages.
+    static constexpr int kCtasPerSm = (MODE == kFp8 && UMMA_FP8_TWO_CTAS) ? 2 : 1;
+    static constexpr int kStages = kCtasPerSm == 2 ? 2 : 4;
     static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int kTmemCols = T::kScaled ? 512 : BN;
     static constexpr int kSfColBase = BN;  // scale columns follow the accumulator
@@ -111,12 +120,13 @@ __device__ __forceinline__ void mma_scaled(uint32_t tmem_d, uint64_t adesc, uint
 }
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, UmmaCfg<BN, MODE>::kCtasPerSm)
 qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const UmmaParams p) {
     using Cfg = UmmaCfg<BN, MODE>;
     using T = ModeTraits<MODE>;
     constexpr int NB = BN / 128;  // 128-row blocks of Bt per tile
+    constexpr int kStages = Cfg::kStages;
     extern __shared__ unsigned char smem_raw[];
     // 128-byte-swizzled tiles must start on a 1024-byte boundary
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});

@@ -327,6 +327,7 @@ def run_ours(args) -> None:
     ms_stack = s0.elapsed_time(s1)
 
     status = sk._C.device_status()
+    launches_per_pass, stack_bytes = stack.launches_per_pass, stack.bytes_per_pass()
     if world > 1:
         t = torch.tensor([ms_total, ms_e2e, float(status), ms_stack], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -348,6 +349,12 @@ def run_ours(args) -> None:
         top = max(MS, key=lambda m: ms_by_m[m])
         achieved = by_m[top]["gbps"]
         traffic = NCU_TRAFFIC_RATIO.get(by_m[top]["kernel"])
+        secondary = None
+        if world == 1 and not args.no_cpu:
+            del stack, sgraph
+            torch.cuda.empty_cache()
+            secondary = secondary_gemms()
+            assert sk._C.device_status() == 0, "a kernel reported a device status in the secondary GEMMs"
         cpu = None
         if world == 1 and not args.no_cpu:
             gbs, secs, used, sample = cpu_sample(0)
@@ -370,10 +377,11 @@ def run_ours(args) -> None:
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "tp_stack": {"workload": "llama3_8b_projection_stack_int4 (32 layers x qkv,o,gate_up,down; M=64)",
-                         "value": round(stack.bytes_per_pass() * args.steps / (ms_stack * 1e-3) / 1e9, 2), "unit": "GB/s",
+                         "value": round(stack_bytes * args.steps / (ms_stack * 1e-3) / 1e9, 2), "unit": "GB/s",
                          "ms_per_pass": round(ms_stack / args.steps, 4), "parallelism": f"tp{tp}",
-                         "allreduces_per_pass": 0 if world == 1 else 2 * 32, "launches_per_pass": stack.launches_per_pass},
-            "gpu_launches": (launches_per_step + stack.launches_per_pass) * args.steps,
+                         "allreduces_per_pass": 0 if world == 1 else 2 * 32, "launches_per_pass": launches_per_pass},
+            "secondary": secondary,
+            "gpu_launches": (launches_per_step + launches_per_pass) * args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -390,7 +398,7 @@ def run_ours(args) -> None:
         os._exit(0)
 
 
-def run_one_gemm(args) -> None:
+def time_one_gemm(kind: str, d0: int, d1: int, d2: int, steps: int, use_graph: bool) -> dict:
     """A small case for ncu and for the secondary GEMMs: one shape through the public op, a few
     launches, timed with CUDA events. w4: K,N,M over 4 weight copies (larger than L2 together for the
     Llama shapes). fp8 / fp8block / mxfp8 / nvfp4 / mxfp4: M,N,K (weights rotated past L2 when M <= 64)."""
@@ -398,11 +406,8 @@ def run_one_gemm(args) -> None:
 
     import spark_kernels as sk
 
-    d0, d1, d2 = (int(v) for v in args.one_gemm.split(","))
-    torch.cuda.set_device(0)
-    sk._C.init()
     g = torch.Generator(device="cuda").manual_seed(0)
-    if args.kind == "w4":
+    if kind == "w4":
         K, N, M = d0, d1, d2
         ws = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 16, 2 * K), dtype=torch.int32, device="cuda", generator=g),
                (torch.rand(K // 128, N, device="cuda", generator=g) * 0.02).to(torch.bfloat16)) for _ in range(4)]
@@ -416,22 +421,22 @@ def run_one_gemm(args) -> None:
         # decode shapes stream the weights: rotate over enough copies to exceed L2 (126 MB)
         copies = 1 if M > 64 else max(2, -(-(300 << 20) // (N * K)))
         bs = [torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(copies)]
-        if args.kind == "fp8":
+        if kind == "fp8":
             qa, sa = sk.fp8_quantize(a, "tensor")
             qs = [sk.fp8_quantize(b, "tensor") for b in bs]
             calls = [lambda q=q: sk.fp8gemm(qa, q[0], sa, q[1]) for q in qs]
-        elif args.kind == "fp8block":  # fp32 scales: 1 x 128 blocks of A, 128 x 128 blocks of B
+        elif kind == "fp8block":  # fp32 scales: 1 x 128 blocks of A, 128 x 128 blocks of B
             qa, sa = sk.fp8_quantize_block128(a.float(), 1)
             qs = [sk.fp8_quantize_block128(b.float(), 128) for b in bs]
             calls = [lambda q=q: sk.fp8gemm_block128(qa, q[0], sa, q[1]) for q in qs]
-        elif args.kind == "mxfp8":
+        elif kind == "mxfp8":
             qa, sfa = sk.fp8_quantize(a, "mx")
             qs = [sk.fp8_quantize(b, "mx") for b in bs]
             calls = [lambda q=q: sk.fp8gemm(qa, q[0], sfa=sfa, sfb=q[1]) for q in qs]
         else:
-            qa, sfa, sa = sk.fp4_quantize(a, args.kind)
-            qs = [sk.fp4_quantize(b, args.kind) for b in bs]
-            if args.kind == "mxfp4":
+            qa, sfa, sa = sk.fp4_quantize(a, kind)
+            qs = [sk.fp4_quantize(b, kind) for b in bs]
+            if kind == "mxfp4":
                 calls = [lambda q=q: sk.fp4gemm(qa, q[0], sfa, q[1], fmt="mxfp4") for q in qs]
             else:
                 calls = [lambda q=q: sk.fp4gemm(qa, q[0], sfa, q[1], fmt="nvfp4", scale_a=sa.reshape(1), scale_b=q[2].reshape(1))
@@ -439,14 +444,14 @@ def run_one_gemm(args) -> None:
         del bs
         work, unit = 2 * M * N * K, "TFLOP/s"
         # the reference's traffic model (scripts/shape_utils.py:342-345): operands + block scales + bf16 output
-        per_elem = {"fp8": 1.0, "fp8block": 1.0, "mxfp8": 1.0 + 1 / 32, "nvfp4": 0.5 + 1 / 16, "mxfp4": 0.5 + 1 / 32}[args.kind]
+        per_elem = {"fp8": 1.0, "fp8block": 1.0, "mxfp8": 1.0 + 1 / 32, "nvfp4": 0.5 + 1 / 16, "mxfp4": 0.5 + 1 / 32}[kind]
         stream_bytes = (M * K + K * N) * per_elem + 2 * M * N
     for i in range(3):
         calls[i % len(calls)]()
     torch.cuda.synchronize()
-    n = max(1, args.steps)
+    n = max(1, steps)
     timing = "eager launches, CUDA events"
-    if args.graph:
+    if use_graph:
         # the launches of one pass captured in a CUDA graph: what a decode engine replays
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -464,7 +469,7 @@ def run_one_gemm(args) -> None:
         timing = "CUDA graph of the launches, CUDA events"
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    if args.graph:
+    if use_graph:
         graph.replay()
     else:
         for i in range(n):
@@ -473,10 +478,43 @@ def run_one_gemm(args) -> None:
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / n
     rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-    extra = {} if args.kind == "w4" else {"gbps": round(stream_bytes / (ms * 1e-3) / 1e9, 1)}
-    print(json.dumps({"one_gemm": [d0, d1, d2], "kind": args.kind, "launches": 3 + n, "us_per_launch": round(ms * 1e3, 2),
+    extra = {} if kind == "w4" else {"gbps": round(stream_bytes / (ms * 1e-3) / 1e9, 1)}
+    return {"one_gemm": [d0, d1, d2], "kind": kind, "launches": 3 + n, "us_per_launch": round(ms * 1e3, 2),
                       "rate": round(rate, 1), "unit": unit, **extra, "timing": timing,
-                      "status": sk._C.device_status()}))
+                      "status": sk._C.device_status()}
+
+
+def run_one_gemm(args) -> None:
+    import torch
+
+    import spark_kernels as sk
+
+    d0, d1, d2 = (int(v) for v in args.one_gemm.split(","))
+    torch.cuda.set_device(0)
+    sk._C.init()
+    print(json.dumps(time_one_gemm(args.kind, d0, d1, d2, args.steps, args.graph)))
+
+
+def secondary_gemms() -> list:
+    """The fp8 / NVFP4 rows of the headline metric (BASELINE configs 2 and 3), measured in the same
+    run: the 8192^3 GEMMs against the tensor peak and the 16 x 4096 x 4096 decode GEMMs as weight
+    streams. The tensor denominators are multiples of the measured dense bf16 rate (fp8 runs at twice,
+    fp4 at four times the bf16 rate on this part)."""
+    try:
+        bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        src = "measured bf16 x"
+    except Exception:
+        bf16, src = 1590.0, "fallback bf16 x"
+    hbm, _ = measured_peak()
+    rows = []
+    for kind, mult in (("fp8", 2), ("fp8block", 2), ("nvfp4", 4)):
+        r = time_one_gemm(kind, 8192, 8192, 8192, 10, False)
+        rows.append({"kind": kind, "shape": [8192, 8192, 8192], "us": r["us_per_launch"], "tflops": r["rate"],
+                     "frac": round(r["rate"] / (mult * bf16), 3), "peak": f"{src}{mult}", "timing": r["timing"]})
+        r = time_one_gemm(kind, 16, 4096, 4096, 40, True)
+        rows.append({"kind": kind, "shape": [16, 4096, 4096], "us": r["us_per_launch"], "gbps": r["gbps"],
+                     "frac": round(r["gbps"] / hbm, 3), "peak": "hbm", "timing": r["timing"]})
+    return rows
 
 
 def main() -> None:
@@ -485,7 +523,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline and the secondary (fp8 / fp4) legs")
     ap.add_argument("--one-gemm", default="", metavar="A,B,C",
                     help="profiling helper: run --steps launches of one GEMM shape through the public op and exit")
     ap.add_argument("--kind", default="w4", choices=["w4", "fp8", "fp8block", "mxfp8", "nvfp4", "mxfp4"],
