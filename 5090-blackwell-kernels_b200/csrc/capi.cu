@@ -46,6 +46,7 @@ int device_state(DeviceState** out) {
             SPK_CUDA(cudaMalloc(&d.partials, kPartialFloats * sizeof(float)));
             SPK_CUDA(cudaMalloc(&d.counters, kCounters * sizeof(unsigned)));
             SPK_CUDA(cudaMalloc(&d.status, kStatusWords * sizeof(int)));
+            SPK_CUDA(cudaMalloc(&d.act_scratch, kActScratchBytes));
             SPK_CUDA(cudaMemset(d.partials, 0, kPartialFloats * sizeof(float)));
             SPK_CUDA(cudaMemset(d.counters, 0, kCounters * sizeof(unsigned)));
             SPK_CUDA(cudaMemset(d.status, 0, kStatusWords * sizeof(int)));

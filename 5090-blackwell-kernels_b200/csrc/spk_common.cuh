@@ -54,12 +54,14 @@ struct DeviceState {
     float* partials = nullptr;      // kPartialFloats fp32, zero between launches
     unsigned* counters = nullptr;   // kCounters, zero between launches
     int* status = nullptr;          // kStatusWords device ints: [0] first error code of a kernel
+    unsigned char* act_scratch = nullptr;  // kActScratchBytes: re-ordered activations of one GEMM
     bool ready = false;
 };
 
 constexpr int64_t kPartialFloats = int64_t{64} * 65536;  // 64 tokens x 65536 columns, 16 MiB
 constexpr int kCounters = 1 << 16;
 constexpr int kStatusWords = 8;
+constexpr int64_t kActScratchBytes = int64_t{64} * 32768 * 2;  // 64 tokens x 32768 k of bf16, 4 MiB
 
 // State of the current device; *out stays valid for the life of the process.
 int device_state(DeviceState** out);

@@ -14,17 +14,19 @@
 // quads 8c + 4(r & 1) + 32(r >> 1) + {0..3}, r = 0..3, of a 64-k unit. tcgen05.st.16x256b places
 // lane (g, c)'s registers at rows g / g + 8 and 32-bit columns 2c, 2c + 1 of each 8-column block,
 // i.e. block r (one K = 16 MMA step) position 4c + i holds k = 8c + 4(r & 1) + 32(r >> 1) + i.
-// The activation tile is therefore written with the same order: the producers copy the token
-// rows in 8-byte pieces (cp.async) to the permuted position, in the 128-byte-swizzled K-major
-// layout, and the tensor core contracts position against position.
+// The activations are therefore put in the same order: a small kernel in front re-orders the
+// 8-byte pieces of every 128-byte unit row into the per-device scratch (16 k-steps of a unit become
+// 4 (r) x 4 (c) quads), tiled TMA loads bring the re-ordered rows in, and the tensor core contracts
+// position against position. (Re-ordering inside the GEMM with 8-byte cp.async copies was measured:
+// two producer warps became the bound above 24 tokens.)
 //
 // One persistent CTA per SM owns a contiguous range of (128-column super-strip, 2-group chunk)
-// units. Roles (23 warps):
+// units. Roles (22 warps):
 //   warps 0-15  dequant: strip 2 (w % 4) + (w / 4) % 2 (its 16 TMEM lanes lie in the lane quarter
 //               w % 4 that the warp may access), chunks of parity w / 8 of the CTA's sequence
 //   warps 16-19 epilogue (TMEM lane quarter w % 4)
 //   warp 20     MMA: loop warp-wide, one elected lane issues 16 tcgen05.mma per chunk
-//   warps 21-22 activation producers (unit w % 2 of every group)
+//   warp 21     activation producer (one elected lane, two TMA loads per group)
 // TMEM columns: accumulators at 0 and NT (double buffered), weights at 128 + 128 cs + 64 sub +
 // 32 h + 8 r for chunk stage cs (3), group sub, unit h, MMA step r.
 #include <algorithm>
@@ -49,15 +51,12 @@ constexpr int DW = kStrips * kSets;
 constexpr int kChunkStages = 3;   // chunks of dequantized weights resident in TMEM
 constexpr int kCodeSlots = 3;     // per-warp ring of one-chunk code pieces
 constexpr int kActStages = 4;     // one group per slot
-constexpr int kActInFlight = 3;   // cp.async groups a producer keeps in flight
 constexpr int kEpilogueWarp0 = DW, kMmaWarp = DW + 4, kProducerWarp0 = DW + 5;
-constexpr int kProducers = 2;     // activation producer warps: unit (w & 1); with 4, rows are split by (w >> 1) too
-constexpr int kThreadsT = (DW + 5 + kProducers) * 32;
+constexpr int kThreadsT = (DW + 6) * 32;
 constexpr int kTmemColsT = 512;
 constexpr int kWeightCol0 = 128;  // first TMEM column of the weight stages
 
 struct W4TmemParams {
-    const unsigned char* A;  // activations bf16 [M][K]
     const unsigned char* packed;
     const unsigned char* scales;
     const unsigned char* zeros;
@@ -81,14 +80,6 @@ struct W4TmemSmem {
 
 __device__ __forceinline__ void cp_async16_t(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8_t(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit_t() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait_t() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive_t(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(ptx::smem_u32(bar)) : "memory");
@@ -115,14 +106,14 @@ __device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uin
 }
 
 template <int NT, bool ASYM>
-__global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const W4TmemParams p) {
+__global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_constant__ CUtensorMap map_act, const W4TmemParams p) {
     using L = W4TmemSmem<NT, ASYM>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
     unsigned char* acts = base;
     unsigned char* codes = acts + kActStages * L::kActBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(codes + L::kCodeRing);
-    uint64_t* act_full = bars;                    // [AS] one arrive per producer warp
+    uint64_t* act_full = bars;                    // [AS] TMA
     uint64_t* act_empty = act_full + kActStages;  // [AS] MMA commit
     uint64_t* a_ready = act_empty + kActStages;   // [CS] the 8 dequant warps of the chunk's set
     uint64_t* a_free = a_ready + kChunkStages;    // [CS] MMA commit
@@ -140,7 +131,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const W4TmemParam
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kActStages; ++s) {
-            mbar_init(&act_full[s], kProducers);
+            mbar_init(&act_full[s], 1);
             mbar_init(&act_empty[s], 1);
         }
         for (int s = 0; s < kChunkStages; ++s) {
@@ -153,6 +144,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const W4TmemParam
         }
         for (int i = 0; i < DW * kCodeSlots; ++i) mbar_init(&code_bar[i], L::kCodeArrivals);
         ptx::fence_mbar_init();
+        umma::prefetch_tensormap(&map_act);
     }
     if (warp == kMmaWarp) umma::tmem_alloc(tmem_slot, kTmemColsT);
     umma::fence_before_sync();
@@ -251,60 +243,26 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const W4TmemParam
             cs += kSets;
             if (cs >= kChunkStages) cs -= kChunkStages, ph ^= 1u;
         }
-    } else if (warp >= kProducerWarp0) {
-        // ================= activation producers: unit h of every group, 8-byte pieces permuted =================
-        const int h = (warp - kProducerWarp0) & 1;
-        const int sp = lane & 15;                              // source piece of the 128-byte unit row
-        constexpr int kRowStep = kProducers;                   // rows a warp covers per pass: 2 per lane half x warps per unit
-        const int t0 = 2 * ((warp - kProducerWarp0) >> 1) + (lane >> 4);  // this lane's rows: t0, t0 + kRowStep, ...
-        const int r = ((sp >> 3) << 1) | (sp & 1), c = (sp >> 1) & 3;
-        const int dp = 4 * r + c;                              // destination piece
-        const uint32_t acts_u32 = ptx::smem_u32(acts) + h * (NT * 128) + (dp & 1) * 8;
-        uint32_t sw[8 / kRowStep];                             // row offset + swizzled chunk of rows t0 + kRowStep j (< 8)
-#pragma unroll
-        for (int j = 0; j < 8 / kRowStep; ++j) {
-            const int t = t0 + kRowStep * j;
-            sw[j] = t * 128 + (((dp >> 1) ^ t) << 4);
-        }
-        const unsigned char* src_lane = p.A + h * 128 + sp * 8;
-        const size_t row_bytes = static_cast<size_t>(p.K) * 2;
-        const int n_groups = n_chunks * kChunkGroups;
-        int s = 0, sig = 0, sig_s = 0, ch = f0 % chunks, sub = 0;
+    } else if (warp == kProducerWarp0) {
+        // ================= activation producer: one 128-k group (two units) per slot =================
+        int s = 0, ch = f0 % chunks;
         unsigned ph = 0;
         bool ok = true;
-        for (int gi = 0; gi < n_groups && ok; ++gi) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&act_empty[s], ph ^ 1u, p.status));
-            if (!ok) break;
-            const unsigned char* src = src_lane + static_cast<size_t>(ch * kChunkGroups + sub) * 256;
-            const uint32_t dst = acts_u32 + s * L::kActBytes;
-            for (int t = t0; t < p.M; t += 8) {  // rows t + kRowStep j differ only in the swizzle term
-#pragma unroll
-                for (int j = 0; j < 8 / kRowStep; ++j)
-                    if (t + kRowStep * j < p.M) cp_async8_t(dst + (t - t0) * 128 + sw[j], src + (t + kRowStep * j) * row_bytes);
-            }
-            cp_async_commit_t();
-            if (gi - sig >= kActInFlight - 1) {
-                cp_async_wait_t<kActInFlight - 1>();
-                ptx::fence_proxy_async();  // cp.async wrote through the generic proxy; the tensor core reads through the async one
+        for (int f = f0; f < f1 && ok; ++f) {
+            for (int sub = 0; sub < kChunkGroups && ok; ++sub) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&act_empty[s], ph ^ 1u, p.status));
+                if (!ok) break;
+                if (umma::elect_one()) {
+                    mbar_arrive_expect_tx(&act_full[s], L::kActBytes);
+                    const int x = (ch * kChunkGroups + sub) * 256;  // byte offset of the group in a token row
+                    umma::tma_load_2d(acts + s * L::kActBytes, &map_act, x, 0, &act_full[s]);
+                    umma::tma_load_2d(acts + s * L::kActBytes + NT * 128, &map_act, x + 128, 0, &act_full[s]);
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&act_full[sig_s]);
-                ++sig;
-                if (++sig_s == kActStages) sig_s = 0;
+                if (++s == kActStages) s = 0, ph ^= 1u;
             }
-            if (++s == kActStages) s = 0, ph ^= 1u;
-            if (++sub == kChunkGroups) {
-                sub = 0;
-                if (++ch == chunks) ch = 0;
-            }
+            if (++ch == chunks) ch = 0;
         }
-        cp_async_wait_t<0>();
-        ptx::fence_proxy_async();
-        __syncwarp();
-        if (ok)
-            for (; sig < n_groups; ++sig) {
-                if (lane == 0) mbar_arrive(&act_full[sig_s]);
-                if (++sig_s == kActStages) sig_s = 0;
-            }
     } else if (warp == kMmaWarp) {
         // ================= MMA issuer: the loop runs warp-wide, one elected lane issues =================
         constexpr uint32_t idesc = umma::instr_desc(128, NT, 1, 1);  // bf16 x bf16 -> f32
@@ -429,12 +387,32 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const W4TmemParam
     if (warp == kMmaWarp) umma::tmem_dealloc(tmem_base, kTmemColsT);
 }
 
+// Re-orders the 8-byte pieces of every 128-byte unit row: destination piece 4 r + c (MMA step r,
+// quad c) comes from source piece 8 (r >> 1) + 2 c + (r & 1). One thread per destination 16 bytes.
+__global__ void __launch_bounds__(256)
+w4_permute_acts_kernel(const uint2* __restrict__ src, uint4* __restrict__ dst, int chunks16) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= chunks16) return;
+    const int m = i & 7, unit = i >> 3;           // 16-byte chunk of the unit row; unit row index
+    const int r = m >> 1, c = (m & 1) * 2;         // destination pieces 2m, 2m + 1 = (r, c), (r, c + 1)
+    const uint2* u = src + static_cast<size_t>(unit) * 16 + 8 * (r >> 1) + 2 * c + (r & 1);
+    const uint2 a = u[0], b = u[2];
+    dst[i] = make_uint4(a.x, a.y, b.x, b.y);
+}
+
 template <int NT, bool ASYM>
-int launch_w4_tmem(W4TmemParams p, DeviceState* dev, cudaStream_t stream) {
+int launch_w4_tmem(const void* A, W4TmemParams p, DeviceState* dev, cudaStream_t stream) {
     using L = W4TmemSmem<NT, ASYM>;
     static_assert(L::kTotal <= 227 * 1024, "w4 tmem kernel exceeds shared memory");
     static_assert(L::kSlotBytes % 16 == 0 && (NT * 128) % 1024 == 0, "slot alignment");
     static_assert(2 * NT <= kWeightCol0 && kWeightCol0 + kChunkStages * 128 <= kTmemColsT, "TMEM column budget");
+    const int chunks16 = p.M * (p.K / 8);
+    w4_permute_acts_kernel<<<cdiv(chunks16, 256), 256, 0, stream>>>(static_cast<const uint2*>(A),
+                                                                    reinterpret_cast<uint4*>(dev->act_scratch), chunks16);
+    SPK_CHECK_LAUNCH();
+    CUtensorMap map_act;
+    if (!umma::make_map_2d_u8(&map_act, dev->act_scratch, static_cast<uint64_t>(p.K) * 2, static_cast<uint64_t>(p.M), NT))
+        return fail(SPK_CUDA_ERROR, "w4gemm: cuTensorMapEncodeTiled failed for M=%d K=%d", p.M, p.K);
     auto kernel = w4_tmem_kernel<NT, ASYM>;
     static bool configured[16] = {};
     if (!configured[dev->device & 15]) {
@@ -444,34 +422,37 @@ int launch_w4_tmem(W4TmemParams p, DeviceState* dev, cudaStream_t stream) {
     p.super_strips = p.N / 128;
     const long long total = static_cast<long long>(p.super_strips) * (p.G / kChunkGroups);
     const int grid = static_cast<int>(std::min<long long>(dev->sm_count, total));
-    kernel<<<grid, kThreadsT, L::kTotal, stream>>>(p);
+    kernel<<<grid, kThreadsT, L::kTotal, stream>>>(map_act, p);
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }
 
 }  // namespace
 
-// Takes min_m <= M <= 64 with N a multiple of 128, an even number of groups and 16-byte-aligned
-// activation rows; `taken` says whether it ran. Off unless SPK_W4_TMEM=1 (SPK_W4_TMEM_MIN_M moves
-// the lower bound, default 1).
+// Takes 16 <= M <= 64 with N a multiple of 128, an even number of groups, 16-byte-aligned activations
+// and M * K within the activation scratch; at exactly 16 tokens only weights of 16 MiB and more (below
+// that the stream kernel's smaller fixed cost wins: 4096 x 4096 13.0 us against 14.9 us). `taken` says
+// whether it ran. Measured on B200, 28672 x 4096 weights, graph-timed, including the re-ordering
+// launch: 16 tokens 32.7 us (stream kernel 37.0), 32 tokens 36.1 (shared-memory-operand kernel 45.7),
+// 64 tokens 46.5 (53.0). SPK_W4_TMEM=0 turns the route off, SPK_W4_TMEM_MIN_M moves the lower bound.
 int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
                     int K, cudaStream_t stream, bool* taken) {
     *taken = false;
     static const int enabled = [] {
         const char* e = std::getenv("SPK_W4_TMEM");
-        return e && *e ? std::atoi(e) : 0;
+        return e && *e ? std::atoi(e) : 1;
     }();
     static const int min_m = [] {
         const char* e = std::getenv("SPK_W4_TMEM_MIN_M");
-        return e && *e ? std::atoi(e) : 1;
+        return e && *e ? std::atoi(e) : 16;
     }();
     if (!enabled || M < min_m || M > 64 || N % 128 != 0 || (K / w4::kGroup) % kChunkGroups != 0) return SPK_OK;
+    if (M == 16 && min_m == 16 && static_cast<int64_t>(K) * N < (int64_t{1} << 25)) return SPK_OK;
     if (static_cast<int64_t>(M) * N > kPartialFloats || (N / 128) * 4 > kCounters) return SPK_OK;
-    if (reinterpret_cast<uintptr_t>(A) % 16 != 0) return SPK_OK;
+    if (reinterpret_cast<uintptr_t>(A) % 16 != 0 || static_cast<int64_t>(M) * K * 2 > kActScratchBytes) return SPK_OK;
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;
     W4TmemParams p{};
-    p.A = static_cast<const unsigned char*>(A);
     p.packed = reinterpret_cast<const unsigned char*>(packed);
     p.scales = static_cast<const unsigned char*>(scales);
     p.zeros = zeros;
@@ -481,12 +462,12 @@ int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, co
     *taken = true;
     const int nt = M <= 16 ? 16 : M <= 32 ? 32 : 64;
     if (zeros)
-        return nt == 16 ? launch_w4_tmem<16, true>(p, dev, stream)
-               : nt == 32 ? launch_w4_tmem<32, true>(p, dev, stream)
-                          : launch_w4_tmem<64, true>(p, dev, stream);
-    return nt == 16 ? launch_w4_tmem<16, false>(p, dev, stream)
-           : nt == 32 ? launch_w4_tmem<32, false>(p, dev, stream)
-                      : launch_w4_tmem<64, false>(p, dev, stream);
+        return nt == 16 ? launch_w4_tmem<16, true>(A, p, dev, stream)
+               : nt == 32 ? launch_w4_tmem<32, true>(A, p, dev, stream)
+                          : launch_w4_tmem<64, true>(A, p, dev, stream);
+    return nt == 16 ? launch_w4_tmem<16, false>(A, p, dev, stream)
+           : nt == 32 ? launch_w4_tmem<32, false>(A, p, dev, stream)
+                      : launch_w4_tmem<64, false>(A, p, dev, stream);
 }
 
 }  // namespace spk

@@ -50,13 +50,13 @@ def alg_bytes(M: int, N: int, K: int) -> int:
 
 
 def kernel_for(m: int) -> str:
-    """The kernel the default route launches for m tokens (w4gemm.cu / w4gemm_umma.cu)."""
-    return "w4_umma_kernel" if 16 < m <= 64 else "w4_stream_kernel"
+    """The kernel the default route launches for m tokens on the Llama MLP shapes (w4gemm.cu, w4gemm_tmem.cu)."""
+    return "w4_tmem_kernel" if 16 <= m <= 64 else "w4_stream_kernel"
 
 
 # DRAM bytes moved per algorithmic byte, from one ncu capture per kernel (dram__bytes_read.sum +
 # dram__bytes_write.sum over the launch's algorithmic bytes; the captures are summarised under profiles/).
-NCU_TRAFFIC_RATIO = {"w4_umma_kernel": 1.031, "w4_stream_kernel": 1.005}
+NCU_TRAFFIC_RATIO = {"w4_tmem_kernel": 1.033, "w4_stream_kernel": 1.005}
 
 
 def step_bytes(layers: int) -> int:
@@ -381,7 +381,9 @@ def run_ours(args) -> None:
                          "ms_per_pass": round(ms_stack / args.steps, 4), "parallelism": f"tp{tp}",
                          "allreduces_per_pass": 0 if world == 1 else 2 * 32, "launches_per_pass": launches_per_pass},
             "secondary": secondary,
-            "gpu_launches": (launches_per_step + launches_per_pass) * args.steps,
+            # the tcgen05 int4 route is two launches per GEMM (activation re-ordering + GEMM)
+            "gpu_launches": (sum(2 * LAYERS * (2 if kernel_for(m) == "w4_tmem_kernel" else 1) for m in MS)
+                             + 2 * launches_per_pass) * args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
