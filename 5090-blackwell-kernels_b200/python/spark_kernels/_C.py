@@ -509,3 +509,61 @@ def fits_l2(nbytes: int, device: str = "") -> bool:
 
 def decode_force_split_k(split: int) -> None:
     _lib.spk_decode_force_split_k(split)
+
+
+# ---- push all-reduce across the GPUs of one node (no counterpart in the reference) ---------------
+
+_sig("spk_comm_buffer_bytes", [_i, ctypes.c_longlong], ctypes.c_longlong)
+_sig("spk_comm_alloc", [ctypes.c_longlong, ctypes.POINTER(_p)])
+_sig("spk_comm_free", [_p])
+_sig("spk_comm_export", [_p, ctypes.c_char_p])
+_sig("spk_comm_open", [ctypes.c_char_p, ctypes.POINTER(_p)])
+_sig("spk_comm_close", [_p])
+_sig("spk_comm_status", [_p, ctypes.POINTER(_i)])
+_sig("spk_allreduce_push_bf16", [_p, ctypes.c_longlong, ctypes.POINTER(_p), _i, _i, ctypes.c_longlong, _p])
+
+
+def comm_alloc(world: int, slot_elems: int) -> int:
+    """A zeroed device buffer for `world` ranks and tensors of up to slot_elems bf16 elements."""
+    nbytes = _lib.spk_comm_buffer_bytes(world, slot_elems)
+    _check(nbytes > 0, f"comm_alloc: world={world} slot_elems={slot_elems} not supported")
+    ptr = _p()
+    _status(_lib.spk_comm_alloc(nbytes, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def comm_free(ptr: int) -> None:
+    _status(_lib.spk_comm_free(ptr))
+
+
+def comm_export(ptr: int) -> bytes:
+    buf = ctypes.create_string_buffer(64)
+    _status(_lib.spk_comm_export(ptr, buf))
+    return buf.raw
+
+
+def comm_open(handle: bytes) -> int:
+    _check(len(handle) == 64, "comm_open: a CUDA IPC handle is 64 bytes")
+    ptr = _p()
+    _status(_lib.spk_comm_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def comm_close(ptr: int) -> None:
+    _status(_lib.spk_comm_close(ptr))
+
+
+def comm_status(local_ptr: int) -> int:
+    code = _i(0)
+    _status(_lib.spk_comm_status(local_ptr, ctypes.byref(code)))
+    return code.value
+
+
+def allreduce_push(t: torch.Tensor, ptrs, rank: int, slot_elems: int) -> torch.Tensor:
+    """In-place sum of the contiguous bf16 tensor t over the ranks whose buffers are `ptrs`."""
+    _check_cuda_contig(t, "t")
+    _check(t.dtype == torch.bfloat16, "allreduce_push: bf16 only")
+    arr = (_p * len(ptrs))(*ptrs)
+    with torch.cuda.device(t.device):
+        _status(_lib.spk_allreduce_push_bf16(t.data_ptr(), t.numel(), arr, rank, len(ptrs), slot_elems, _stream(t)))
+    return t

@@ -112,3 +112,51 @@ class ProjectionStack:
                 sk.w4gemm(self.x[name], packed, scales, None, -1, self.y[name])
                 if all_reduce is not None and name in ("o", "down"):
                     all_reduce(self.y[name])
+
+
+class PushAllReduce:
+    """All-reduce (sum) of small bf16 tensors over the ranks of a one-node process group by direct
+    peer stores: every rank owns a buffer in device memory, the ranks exchange CUDA IPC handles of
+    their buffers once through the process group, and each call is one kernel per rank that writes
+    the local tensor into every peer's buffer, waits for the peers' writes to land in its own, and
+    sums them in rank order (the same bits on all ranks). Safe to capture in a CUDA graph: the call
+    counter lives on the device. All ranks must call it the same number of times with the same sizes.
+
+        ar = PushAllReduce(sk, group=None, max_elems=64 * 4096, device=dev)
+        ar(y)            # y: contiguous bf16, numel % 8 == 0, numel <= max_elems
+        ar.close()
+    """
+
+    def __init__(self, sk, group, max_elems: int, device):
+        import torch.distributed as dist
+
+        self._C, self.group, self.slot_elems = sk._C, group, int(max_elems)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.device = torch.device(device)
+        with torch.cuda.device(self.device):
+            self.local = self._C.comm_alloc(self.world, self.slot_elems)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, self._C.comm_export(self.local), group=group)
+            self.ptrs = [self.local if r == self.rank else self._C.comm_open(handles[r]) for r in range(self.world)]
+        dist.barrier(group)
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        return self._C.allreduce_push(t, self.ptrs, self.rank, self.slot_elems)
+
+    def status(self) -> int:
+        """0, or the status a bounded wait for a peer left behind (synchronizes the device)."""
+        with torch.cuda.device(self.device):
+            return self._C.comm_status(self.local)
+
+    def close(self) -> None:
+        import torch.distributed as dist
+
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            dist.barrier(self.group)  # nobody closes a buffer a peer may still be writing to
+            for r, ptr in enumerate(self.ptrs):
+                if r != self.rank:
+                    self._C.comm_close(ptr)
+            dist.barrier(self.group)
+            self._C.comm_free(self.local)
+        self.ptrs = []

@@ -188,6 +188,22 @@ def run_ours(args) -> None:
     tp = world
     assert (2 * INTER) % (16 * tp) == 0 and INTER % (128 * tp) == 0
     sk._C.init()
+    # the all-reduce after the row-split GEMMs: direct peer stores (one kernel per rank), or NCCL
+    reduce, reduce_name = None, "none"
+    if world > 1:
+        reduce, reduce_name = (lambda t: dist.all_reduce(t)), "nccl"
+        if args.allreduce == "push":
+            try:
+                from spark_kernels import tp as tpmod_
+
+                pusher = tpmod_.PushAllReduce(sk, None, 64 * HIDDEN, dev)
+                reduce, reduce_name = pusher, "push (peer stores over NVLink, one kernel per rank)"
+            except Exception as e:  # CUDA IPC can be closed to a container; NCCL then carries the sum
+                reduce_name = f"nccl (push unavailable: {type(e).__name__})"
+            ok_all = torch.tensor([1.0 if reduce_name.startswith("push") else 0.0], device=dev)
+            dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+            if ok_all.item() < 1.0 and reduce_name.startswith("push"):
+                reduce, reduce_name = (lambda t: dist.all_reduce(t)), "nccl (push unavailable on a peer)"
 
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
 
@@ -212,7 +228,7 @@ def run_ours(args) -> None:
             sk.w4gemm(h[m], dn[layer][0], dn[layer][1], None, -1, y_dn[m])
             n += 2
             if world > 1:
-                dist.all_reduce(y_dn[m])
+                reduce(y_dn[m])
         return n
 
     # eager warm-up on a side stream, then capture one graph per token count; a step replays all of them
@@ -306,7 +322,7 @@ def run_ours(args) -> None:
     from spark_kernels import tp as tpmod
 
     stack = tpmod.ProjectionStack(sk, tpmod.LlamaShape(), 64, rank, tp, dev, seed=99)
-    reduce_fn = (lambda t: dist.all_reduce(t)) if world > 1 else None
+    reduce_fn = reduce
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         stack.run(reduce_fn)
@@ -366,7 +382,7 @@ def run_ours(args) -> None:
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint4->fp32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers": LAYERS, "M": list(MS), "gate_up": [2 * INTER, HIDDEN],
-                       "down": [HIDDEN, INTER], "group": 128, "parallelism": f"tp{tp}",
+                       "down": [HIDDEN, INTER], "group": 128, "parallelism": f"tp{tp}", "allreduce": reduce_name,
                        "l2": "inputs larger than L2 (1.4 GB of weights per step)", "launch": "cuda graph"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": which,
@@ -525,6 +541,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--allreduce", default="push", choices=["push", "nccl"],
+                    help="N > 1: how the row-split GEMMs' outputs are summed")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline and the secondary (fp8 / fp4) legs")
     ap.add_argument("--one-gemm", default="", metavar="A,B,C",
                     help="profiling helper: run --steps launches of one GEMM shape through the public op and exit")

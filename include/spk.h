@@ -159,6 +159,25 @@ SPK_API int spk_decode_fits_l2(int64_t bytes, int device);
 SPK_API void spk_decode_force_split_k(int split);
 SPK_API int spk_decode_forced_split_k(void);
 
+/* ---- push all-reduce for the row-split projections of a tensor-parallel layer ---------------
+ * No counterpart in the reference (it is single GPU). One process per GPU of one node: every rank
+ * allocates a buffer with spk_comm_alloc (spk_comm_buffer_bytes(world, slot_elems) bytes, zeroed),
+ * exports it (64-byte CUDA IPC handle), opens the handles of its peers, and passes the world
+ * pointers (its own at index rank) to every call. spk_allreduce_push_bf16 sums `n` bf16 elements
+ * (n % 8 == 0, n <= slot_elems) in place over all ranks, in rank order in fp32, one rounding: the
+ * same bits on every rank. All ranks must make the same sequence of calls. world <= 8. A wait for
+ * a peer that does not arrive within about a second sets the status word read by spk_comm_status
+ * (SPK_TIMEOUT) and leaves the data unsummed. */
+SPK_API long long spk_comm_buffer_bytes(int world, long long slot_elems);
+SPK_API int spk_comm_alloc(long long bytes, void** ptr);
+SPK_API int spk_comm_free(void* ptr);
+SPK_API int spk_comm_export(void* ptr, unsigned char* handle64);
+SPK_API int spk_comm_open(const unsigned char* handle64, void** ptr);
+SPK_API int spk_comm_close(void* ptr);
+SPK_API int spk_comm_status(void* local_buf, int* code);
+SPK_API int spk_allreduce_push_bf16(void* data, long long n, void* const* bufs, int rank, int world,
+                                    long long slot_elems, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
