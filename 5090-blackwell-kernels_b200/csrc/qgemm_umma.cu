@@ -548,8 +548,8 @@ bool decode_fits(const simt::Params& p, size_t scratch_bytes_before) {
 // The tensor core has no fp32 block scaling, so every 128-k block is contracted on its own into a
 // TMEM buffer (4 MMAs of K = 32, the first one overwriting) and the epilogue warps fold it into fp32
 // register accumulators with the block's two scales: acc += (sA[m][kb] * sB[n / 128][kb]) * block.
-// Two TMEM buffers let the folding of block kb overlap the MMAs of block kb + 1. One CTA per
-// 128 x 128 tile (one sB per block and tile); a thread owns one row and its 128 accumulators.
+// Two TMEM buffers let the folding of block kb overlap the MMAs of block kb + 1. A folding thread
+// owns one row of one 128-column half of the tile (one sB per block and half) and its 128 accumulators.
 struct Block128Params {
     __nv_bfloat16* C;
     int M, N, K;
@@ -558,19 +558,32 @@ struct Block128Params {
     int* status;
 };
 
-constexpr int kBlkStages = 4, kBlkBN = 128;
-constexpr int kBlkStageBytes = (kBM + kBlkBN) * kBKBytes;
-constexpr int kBlkSmem = kBlkStages * kBlkStageBytes + 1024 + 256;
+constexpr int kBlkStages = 4;
 
-__global__ void __launch_bounds__(192, 1)
+template <int BN>
+struct BlkCfg {
+    static constexpr int kHalves = BN / 128;                 // 128-column halves of the tile = sB blocks per k-block
+    static constexpr int kThreads = 64 + 128 * kHalves;      // producer, MMA, 4 epilogue warps per half
+    static constexpr int kStageBytes = (kBM + BN) * kBKBytes;
+    static constexpr int kSmem = kBlkStages * kStageBytes + 1024 + 256;
+    static constexpr int kTmemCols = 2 * BN;                  // two buffers
+};
+
+// One CTA per 128 x BN tile, BN = 128 or 256. Epilogue warp e (0 .. 4 kHalves - 1) owns the 32 rows of
+// TMEM lane quarter (e + 2) % 4 and the 128 columns of half e / 4: 128 fp32 accumulators per thread.
+// (Packed f32x2 FMAs in the fold were tried and changed nothing: the fold waits on its four
+// tcgen05.ld round trips per block, not on the FMA pipe.)
+template <int BN>
+__global__ void __launch_bounds__(BlkCfg<BN>::kThreads, 1)
 qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            const Block128Params p) {
+    using Cfg = BlkCfg<BN>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kBlkStages * kBlkStageBytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kBlkStages * Cfg::kStageBytes);
     uint64_t* empty = full + kBlkStages;
     uint64_t* tfull = empty + kBlkStages;  // [2] MMA commit: a block's sum is complete in TMEM buffer b
-    uint64_t* tfree = tfull + 2;           // [2] the 4 epilogue warps have read buffer b
+    uint64_t* tfree = tfull + 2;           // [2] every epilogue warp has read buffer b
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfree + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -585,13 +598,13 @@ qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tfree[b], 4);
+            mbar_init(&tfree[b], 4 * Cfg::kHalves);
         }
         ptx::fence_mbar_init();
         umma::prefetch_tensormap(&map_a);
         umma::prefetch_tensormap(&map_b);
     }
-    if (warp == 1) umma::tmem_alloc(tmem_slot, 2 * kBlkBN);
+    if (warp == 1) umma::tmem_alloc(tmem_slot, Cfg::kTmemCols);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -605,16 +618,16 @@ qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, p.status));
             if (!ok) break;
             if (umma::elect_one()) {
-                mbar_arrive_expect_tx(&full[s], kBlkStageBytes);
-                unsigned char* st = tiles + s * kBlkStageBytes;
+                mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+                unsigned char* st = tiles + s * Cfg::kStageBytes;
                 umma::tma_load_2d(st, &map_a, kb * kBKBytes, tile_m * kBM, &full[s]);
-                umma::tma_load_2d(st + kBM * kBKBytes, &map_b, kb * kBKBytes, tile_n * kBlkBN, &full[s]);
+                umma::tma_load_2d(st + kBM * kBKBytes, &map_b, kb * kBKBytes, tile_n * BN, &full[s]);
             }
             __syncwarp();
             if (++s == kBlkStages) s = 0, ph ^= 1u;
         }
     } else if (warp == 1) {
-        constexpr uint32_t idesc = umma::instr_desc(kBM, kBlkBN, 0, 0);  // e4m3 x e4m3 -> f32
+        constexpr uint32_t idesc = umma::instr_desc(kBM, BN, 0, 0);  // e4m3 x e4m3 -> f32
         int s = 0;
         unsigned ph = 0;
         bool ok = true;
@@ -625,12 +638,12 @@ qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             if (!ok) break;
             umma::fence_after_sync();
             if (umma::elect_one()) {
-                const unsigned char* st = tiles + s * kBlkStageBytes;
+                const unsigned char* st = tiles + s * Cfg::kStageBytes;
                 const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + kBM * kBKBytes);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    umma::mma_f8f6f4(tmem_acc + buf * kBlkBN, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k),
-                                     idesc, k > 0);
+                    umma::mma_f8f6f4(tmem_acc + buf * BN, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
+                                     k > 0);
                 umma::mma_commit(&empty[s]);
                 umma::mma_commit(&tfull[buf]);
             }
@@ -638,14 +651,16 @@ qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             if (++s == kBlkStages) s = 0, ph ^= 1u;
         }
     } else {
-        // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1; a thread owns one row ----
-        const int quarter = warp & 3;
+        // ---- epilogue warps: TMEM lane quarter = warp % 4; a thread owns one row of one 128-column half ----
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = tile_m * kBM + quarter * 32 + lane;
+        const int nb = tile_n * Cfg::kHalves + half;  // 128-column block of Bt
+        const bool nb_ok = nb * 128 < p.N;
         const float* sa_row = p.sA + static_cast<size_t>(row < p.M ? row : 0) * KB;
-        const float* sb_row = p.sB + static_cast<size_t>(tile_n) * KB;
-        float acc[kBlkBN];
+        const float* sb_row = p.sB + static_cast<size_t>(nb_ok ? nb : 0) * KB;
+        float acc[128];
 #pragma unroll
-        for (int i = 0; i < kBlkBN; ++i) acc[i] = 0.f;
+        for (int i = 0; i < 128; ++i) acc[i] = 0.f;
         bool ok = true;
         float f_next = KB > 0 ? __ldg(sa_row) * __ldg(sb_row) : 0.f;
         for (int kb = 0; kb < KB && ok; ++kb) {
@@ -655,27 +670,23 @@ qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             ok = __all_sync(0xffffffffu, mbar_wait(&tfull[buf], (kb >> 1) & 1, p.status));
             if (!ok) break;
             umma::fence_after_sync();
-            const uint32_t t0 = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlkBN;
+            const uint32_t t0 = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * 128;
 #pragma unroll
-            for (int c0 = 0; c0 < kBlkBN; c0 += 64) {
-                uint32_t r0[32], r1[32];
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+                uint32_t r0[32];
                 umma::tmem_ld_32x32(t0 + c0, r0);
-                umma::tmem_ld_32x32(t0 + c0 + 32, r1);
                 umma::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    acc[c0 + i] = fmaf(__uint_as_float(r0[i]), f, acc[c0 + i]);
-                    acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), f, acc[c0 + 32 + i]);
-                }
+                for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(__uint_as_float(r0[i]), f, acc[c0 + i]);
             }
             umma::fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tfree[buf]);
         }
-        if (ok && row < p.M) {
+        if (ok && row < p.M && nb_ok) {
 #pragma unroll
-            for (int c0 = 0; c0 < kBlkBN; c0 += 32) {
-                const int col = tile_n * kBlkBN + c0;
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+                const int col = nb * 128 + c0;
                 if (col < p.N) {  // N % 64 == 0: a 32-column run is all in or all out
                     uint4 out[4];
                     uint32_t* o = reinterpret_cast<uint32_t*>(out);
@@ -693,7 +704,30 @@ qgemm_umma_block128_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     }
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 1) umma::tmem_dealloc(tmem_acc, 2 * kBlkBN);
+    if (warp == 1) umma::tmem_dealloc(tmem_acc, Cfg::kTmemCols);
+}
+
+template <int BN>
+int launch_block128(const simt::Params& q, DeviceState* dev, cudaStream_t stream) {
+    using Cfg = BlkCfg<BN>;
+    static_assert(Cfg::kSmem <= 227 * 1024, "stage ring exceeds shared memory");
+    CUtensorMap map_a, map_b;
+    if (!umma::make_map_2d_u8(&map_a, q.A, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M), kBM) ||
+        !umma::make_map_2d_u8(&map_b, q.Bt, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), BN))
+        return fail(SPK_CUDA_ERROR, "fp8gemm_block128: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
+    auto kernel = qgemm_umma_block128_kernel<BN>;
+    static bool configured[16] = {};
+    if (!configured[dev->device & 15]) {
+        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        configured[dev->device & 15] = true;
+    }
+    Block128Params p{};
+    p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
+    p.sA = q.blk_a, p.sB = q.blk_b;
+    p.status = dev->status;
+    kernel<<<cdiv(q.M, kBM) * cdiv(q.N, BN), Cfg::kThreads, Cfg::kSmem, stream>>>(map_a, map_b, p);
+    SPK_CHECK_LAUNCH();
+    return SPK_OK;
 }
 
 // Row-major ue8m0 scales [rows][K/32] (the fp8 MX API layout) -> the blocked layout the tensor core
@@ -786,23 +820,10 @@ int fp8gemm_block128_umma_try(const simt::Params& q, cudaStream_t stream, bool* 
     if (umma_disabled() || !aligned16(q.C)) return SPK_OK;
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;
-    CUtensorMap map_a, map_b;
-    if (!umma::make_map_2d_u8(&map_a, q.A, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M), kBM) ||
-        !umma::make_map_2d_u8(&map_b, q.Bt, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), kBlkBN))
-        return fail(SPK_CUDA_ERROR, "fp8gemm_block128: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
-        SPK_CUDA(cudaFuncSetAttribute(qgemm_umma_block128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBlkSmem));
-        configured[dev->device & 15] = true;
-    }
     *taken = true;
-    Block128Params p{};
-    p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
-    p.sA = q.blk_a, p.sB = q.blk_b;
-    p.status = dev->status;
-    qgemm_umma_block128_kernel<<<cdiv(q.M, kBM) * cdiv(q.N, kBlkBN), 192, kBlkSmem, stream>>>(map_a, map_b, p);
-    SPK_CHECK_LAUNCH();
-    return SPK_OK;
+    // 128 x 256 tiles (8 folding warps) once they fill the SMs; 128 x 128 for small problems
+    const bool wide = q.N % 256 == 0 && static_cast<long long>(cdiv(q.M, kBM)) * (q.N / 256) >= dev->sm_count;
+    return wide ? launch_block128<256>(q, dev, stream) : launch_block128<128>(q, dev, stream);
 }
 
 }  // namespace spk

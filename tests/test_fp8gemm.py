@@ -156,7 +156,8 @@ def test_fp8gemm_block128_matches_oracle(sk, orc):
     """fp32 1x128 / 128x128 block scales: no counterpart in the reference (parity unpinned); the
     CUDA quantizer and GEMM are held to the oracle's definition."""
     rng = np.random.default_rng(6)
-    for (M, N, K) in [(16, 4096, 4096), (4, 256, 512), (130, 192, 384)]:
+    # the last shape has enough 128 x 256 tiles to take the wide-tile kernel
+    for (M, N, K) in [(16, 4096, 4096), (4, 256, 512), (130, 192, 384), (2048, 2560, 256)]:
         a = rng.standard_normal((M, K)).astype(np.float32)
         b = rng.standard_normal((N, K)).astype(np.float32)
         a[0, :128] = 0  # an all-zero block
