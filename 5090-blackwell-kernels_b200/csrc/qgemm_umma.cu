@@ -345,6 +345,7 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     uint64_t* acc_ready = empty + kDecodeStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
 
+    pdl_release();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x % p.n_tiles, sk = blockIdx.x / p.n_tiles;
     const int k_bytes = p.K / T::kElemsPerByte;
@@ -366,25 +367,40 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const uint32_t tmem_acc = *tmem_slot;
 
     if (warp == 0) {
-        int s = 0;
-        unsigned ph = 0;
+        // The launch is chained: the weight tiles of the first stages are requested at once, everything a
+        // kernel in front may still be writing (tokens, their scales, repacked MX scales) after pdl_wait().
+        auto load_weights = [&](int kb, int s) {
+            mbar_arrive_expect_tx(&full[s], Cfg::kTxBytes);
+            umma::tma_load_2d(tiles + s * Cfg::kStageBytes, &map_w, kb * kBKBytes, tile_n * kBM, &full[s]);
+        };
+        auto load_rest = [&](int kb, int s) {
+            unsigned char* st = tiles + s * Cfg::kStageBytes;
+            umma::tma_load_2d(st + Cfg::kWBytes, &map_x, kb * kBKBytes, 0, &full[s]);
+            if (T::kScaled) {
+                unsigned char* sf = st + Cfg::kWBytes + Cfg::kXBytes;
+                const size_t tile0 = static_cast<size_t>(kb) * T::kTiles;
+                bulk_g2s(sf, p.sfw + (static_cast<size_t>(tile_n) * p.sf_tiles_per_rowblock + tile0) * kSfTile, Cfg::kSfBytes,
+                         &full[s]);
+                bulk_g2s(sf + Cfg::kSfBytes, p.sfx + tile0 * kSfTile, Cfg::kSfBytes, &full[s]);
+            }
+        };
+        const int early = kb1 - kb0 < kDecodeStages ? kb1 - kb0 : kDecodeStages;
+        if (umma::elect_one())
+            for (int i = 0; i < early; ++i) load_weights(kb0 + i, i);
+        __syncwarp();
+        pdl_wait();
+        if (umma::elect_one())
+            for (int i = 0; i < early; ++i) load_rest(kb0 + i, i);
+        __syncwarp();
+        int s = early == kDecodeStages ? 0 : early;
+        unsigned ph = early == kDecodeStages ? 1u : 0u;
         bool ok = true;
-        for (int kb = kb0; kb < kb1 && ok; ++kb) {
-            // a fresh barrier passes a wait on the opposite parity, so the first lap does not block
+        for (int kb = kb0 + early; kb < kb1 && ok; ++kb) {
             ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, p.status));
             if (!ok) break;
             if (umma::elect_one()) {
-                mbar_arrive_expect_tx(&full[s], Cfg::kTxBytes);
-                unsigned char* st = tiles + s * Cfg::kStageBytes;
-                umma::tma_load_2d(st, &map_w, kb * kBKBytes, tile_n * kBM, &full[s]);
-                umma::tma_load_2d(st + Cfg::kWBytes, &map_x, kb * kBKBytes, 0, &full[s]);
-                if (T::kScaled) {
-                    unsigned char* sf = st + Cfg::kWBytes + Cfg::kXBytes;
-                    const size_t tile0 = static_cast<size_t>(kb) * T::kTiles;
-                    bulk_g2s(sf, p.sfw + (static_cast<size_t>(tile_n) * p.sf_tiles_per_rowblock + tile0) * kSfTile, Cfg::kSfBytes,
-                             &full[s]);
-                    bulk_g2s(sf + Cfg::kSfBytes, p.sfx + tile0 * kSfTile, Cfg::kSfBytes, &full[s]);
-                }
+                load_weights(kb, s);
+                load_rest(kb, s);
             }
             __syncwarp();
             if (++s == kDecodeStages) s = 0, ph ^= 1u;
@@ -433,6 +449,7 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     } else {
         // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1; lane = weight row n ----
         const int quarter = warp & 3;
+        pdl_wait();  // C, the scale scalars and the split-K scratch may still be in use by the kernel in front
         const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0, p.status));
         umma::fence_after_sync();
         if (ok && kb1 > kb0) {
@@ -525,8 +542,7 @@ int launch_decode(const simt::Params& q, const unsigned char* sfw, const unsigne
     }();
     p.split = std::max(1, std::min(per_sm * dev->sm_count / p.n_tiles, k_blocks / 2));
     p.partials = partials, p.counters = dev->counters, p.status = dev->status;
-    kernel<<<p.n_tiles * p.split, 192, Cfg::kSmem, stream>>>(map_w, map_x, p);
-    SPK_CHECK_LAUNCH();
+    SPK_CUDA(launch_chained(kernel, dim3(p.n_tiles * p.split), dim3(192), Cfg::kSmem, stream, map_w, map_x, p));
     return SPK_OK;
 }
 

@@ -13,6 +13,8 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <utility>
 
 #include "../../include/spk.h"
 
@@ -62,6 +64,41 @@ constexpr int64_t kPartialFloats = int64_t{64} * 65536;  // 64 tokens x 65536 co
 constexpr int kCounters = 1 << 16;
 constexpr int kStatusWords = 8;
 constexpr int64_t kActScratchBytes = int64_t{64} * 32768 * 2;  // 64 tokens x 32768 k of bf16, 4 MiB
+
+// Programmatic dependent launch. A kernel launched through launch_chained() may begin while the
+// kernel before it in the stream is still running, provided that kernel has executed
+// pdl_release() (griddepcontrol.launch_dependents) in all of its blocks; it must then execute
+// pdl_wait() (griddepcontrol.wait: the predecessor has completed and its writes are visible)
+// before it reads anything the predecessor may write or writes anything the predecessor may read.
+// Only kernels of this library release early, so a kernel of this library that follows foreign work
+// starts after that work has completed, as usual. SPK_PDL=0 turns the attribute off.
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("SPK_PDL");
+        return !(e && *e == '0');
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 // State of the current device; *out stays valid for the life of the process.
 int device_state(DeviceState** out);

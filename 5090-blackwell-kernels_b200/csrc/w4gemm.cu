@@ -276,6 +276,7 @@ w4_stream_kernel(const StreamParams p) {
         ptx::fence_mbar_init();
     }
     __syncthreads();  // the only block-wide barrier: barrier objects are ready
+    pdl_release();  // a chained kernel behind this one may become resident as this grid's CTAs exit
     if (n_chunks <= 0) return;
 
     // ---- activation producer state (warp 0 only): chunk j goes to stage j % kActStages, one bulk
@@ -308,8 +309,6 @@ w4_stream_kernel(const StreamParams p) {
             }
         }
     };
-    if (warp == 0) issue_acts(n_chunks < kActLead ? n_chunks : kActLead);
-
     unsigned char* ring = smem + warp * (ST * S::kBytes);
     const size_t strip_bytes = static_cast<size_t>(p.G) * w4::kGroupBytes;
     auto valid_of = [&](int t_first) {
@@ -365,6 +364,11 @@ w4_stream_kernel(const StreamParams p) {
     };
 #pragma unroll 1
     for (int s = 0; s < ST; ++s) issue();
+
+    // The weight stream is under way; everything below reads activations or touches the output and the
+    // split-K scratch, which the kernel in front of a chained launch may still be using.
+    pdl_wait();
+    if (warp == 0) issue_acts(n_chunks < kActLead ? n_chunks : kActLead);
 
     // ---- consumer ----
     float acc[NS][MT][NA][4];
@@ -586,7 +590,7 @@ int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target
     const long long total = static_cast<long long>(p.super_strips) * chunks;
     const long long want = whole ? p.super_strips : std::max<long long>(1, total / std::max(1, min_chunks));
     const dim3 grid(static_cast<unsigned>(std::min(want, slots)), static_cast<unsigned>(m_chunks));
-    kernel<<<grid, kStreamWarps * 32, smem, stream>>>(p);
+    SPK_CUDA(launch_chained(kernel, grid, dim3(kStreamWarps * 32), smem, stream, p));
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }

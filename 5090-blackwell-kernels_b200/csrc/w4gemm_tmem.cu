@@ -20,6 +20,10 @@
 // position against position. (Re-ordering inside the GEMM with 8-byte cp.async copies was measured:
 // two producer warps became the bound above 24 tokens.)
 //
+// The two launches are chained programmatically (spk_common.cuh): the GEMM's CTAs become resident,
+// set up and start streaming weights while the re-ordering kernel (and, SM by SM, the tail of the
+// GEMM before it) is still running; only the activation producer and the epilogue warps wait for it.
+//
 // One persistent CTA per SM owns a contiguous range of (128-column super-strip, 2-group chunk)
 // units. Roles (22 warps):
 //   warps 0-15  dequant: strip 2 (w % 4) + (w / 4) % 2 (its 16 TMEM lanes lie in the lane quarter
@@ -122,6 +126,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     uint64_t* code_bar = acc_free + 2;            // [DW][kCodeSlots]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(code_bar + DW * kCodeSlots);
 
+    pdl_release();  // a chained kernel behind this one may become resident as this grid's CTAs exit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunks = p.G / kChunkGroups;  // chunks per super-strip
     const long long total = static_cast<long long>(p.super_strips) * chunks;
@@ -129,22 +134,27 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     const int f1 = static_cast<int>((blockIdx.x + 1) * total / gridDim.x);
     const int n_chunks = f1 - f0;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kActStages; ++s) {
-            mbar_init(&act_full[s], 1);
-            mbar_init(&act_empty[s], 1);
+    // barrier set-up spread over lanes: every dequant warp its own code barriers, one epilogue warp the rest
+    if (warp < DW) {
+        if (lane < kCodeSlots) {
+            mbar_init(&code_bar[warp * kCodeSlots + lane], L::kCodeArrivals);
+            ptx::fence_mbar_init();
         }
-        for (int s = 0; s < kChunkStages; ++s) {
-            mbar_init(&a_ready[s], kStrips);
-            mbar_init(&a_free[s], 1);
+    } else if (warp == kEpilogueWarp0) {
+        if (lane < kActStages) {
+            mbar_init(&act_full[lane], 1);
+            mbar_init(&act_empty[lane], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_ready[b], 1);
-            mbar_init(&acc_free[b], 4);
+        if (lane < kChunkStages) {
+            mbar_init(&a_ready[lane], kStrips);
+            mbar_init(&a_free[lane], 1);
         }
-        for (int i = 0; i < DW * kCodeSlots; ++i) mbar_init(&code_bar[i], L::kCodeArrivals);
+        if (lane < 2) {
+            mbar_init(&acc_ready[lane], 1);
+            mbar_init(&acc_free[lane], 4);
+        }
         ptx::fence_mbar_init();
-        umma::prefetch_tensormap(&map_act);
+        if (lane == 0) umma::prefetch_tensormap(&map_act);
     }
     if (warp == kMmaWarp) umma::tmem_alloc(tmem_slot, kTmemColsT);
     umma::fence_before_sync();
@@ -245,6 +255,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         }
     } else if (warp == kProducerWarp0) {
         // ================= activation producer: one 128-k group (two units) per slot =================
+        pdl_wait();  // the re-ordered activations are written by the kernel in front of this one
         int s = 0, ch = f0 % chunks;
         unsigned ph = 0;
         bool ok = true;
@@ -312,6 +323,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     } else {
         // ================= epilogue warps: TMEM lane quarter = warp % 4 =================
         const int quarter = warp & 3;
+        pdl_wait();  // C and the split-K scratch may still be in use by the kernels in front
         int pend_ss[2] = {0, 0}, pend_n[2] = {0, 0}, n_pend = 0;
         int seg = 0, seg_ch0 = f0 % chunks;
         bool ok = true;
@@ -391,6 +403,8 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
 // quad c) comes from source piece 8 (r >> 1) + 2 c + (r & 1). One thread per destination 16 bytes.
 __global__ void __launch_bounds__(256)
 w4_permute_acts_kernel(const uint2* __restrict__ src, uint4* __restrict__ dst, int chunks16) {
+    pdl_release();  // the GEMM behind this kernel may start its set-up and weight stream now
+    pdl_wait();     // the source may be the output of the kernel before; the scratch may still be read by it
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i >= chunks16) return;
     const int m = i & 7, unit = i >> 3;           // 16-byte chunk of the unit row; unit row index
@@ -407,9 +421,8 @@ int launch_w4_tmem(const void* A, W4TmemParams p, DeviceState* dev, cudaStream_t
     static_assert(L::kSlotBytes % 16 == 0 && (NT * 128) % 1024 == 0, "slot alignment");
     static_assert(2 * NT <= kWeightCol0 && kWeightCol0 + kChunkStages * 128 <= kTmemColsT, "TMEM column budget");
     const int chunks16 = p.M * (p.K / 8);
-    w4_permute_acts_kernel<<<cdiv(chunks16, 256), 256, 0, stream>>>(static_cast<const uint2*>(A),
-                                                                    reinterpret_cast<uint4*>(dev->act_scratch), chunks16);
-    SPK_CHECK_LAUNCH();
+    SPK_CUDA(launch_chained(w4_permute_acts_kernel, dim3(cdiv(chunks16, 256)), dim3(256), 0, stream, static_cast<const uint2*>(A),
+                            reinterpret_cast<uint4*>(dev->act_scratch), chunks16));
     CUtensorMap map_act;
     if (!umma::make_map_2d_u8(&map_act, dev->act_scratch, static_cast<uint64_t>(p.K) * 2, static_cast<uint64_t>(p.M), NT))
         return fail(SPK_CUDA_ERROR, "w4gemm: cuTensorMapEncodeTiled failed for M=%d K=%d", p.M, p.K);
@@ -422,8 +435,7 @@ int launch_w4_tmem(const void* A, W4TmemParams p, DeviceState* dev, cudaStream_t
     p.super_strips = p.N / 128;
     const long long total = static_cast<long long>(p.super_strips) * (p.G / kChunkGroups);
     const int grid = static_cast<int>(std::min<long long>(dev->sm_count, total));
-    kernel<<<grid, kThreadsT, L::kTotal, stream>>>(map_act, p);
-    SPK_CHECK_LAUNCH();
+    SPK_CUDA(launch_chained(kernel, dim3(grid), dim3(kThreadsT), L::kTotal, stream, map_act, p));
     return SPK_OK;
 }
 

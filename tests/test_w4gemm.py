@@ -169,3 +169,41 @@ def test_w4gemm_in_a_cuda_graph(sk, orc):
         torch.cuda.synchronize()
         assert_bf16_close(out, want, "graph replay")
     assert sk._C.device_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 16, 48, 64])
+def test_w4gemm_back_to_back_calls_chain_correctly(sk, orc, M):
+    """Consecutive launches of the library overlap (the next GEMM's weight stream starts while the
+    previous one finishes). A chain in which every GEMM reads the previous GEMM's output, enqueued
+    without host synchronisation, must give what the same chain gives with a device synchronise
+    between the calls."""
+    K = N = 4096
+    g = torch.Generator(device="cpu").manual_seed(5)
+    # random codes, scales sized so that the chained activations stay O(1)
+    ws = []
+    for i in range(3):
+        w = (torch.randn(K, N, generator=g) * (1.0 / K ** 0.5)).to(torch.bfloat16)
+        ws.append(sk.W4Weight.quantize(w.cuda()))
+    x0 = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+
+    def chain(sync: bool):
+        outs, x = [], x0
+        for rep in range(4):
+            for ww in ws:
+                x = sk.w4gemm(x, ww, variant=2)
+                if sync:
+                    torch.cuda.synchronize()
+                outs.append(x)
+        torch.cuda.synchronize()
+        return outs
+
+    want = chain(True)
+    for attempt in range(5):
+        got = chain(False)
+        for i, (a, b) in enumerate(zip(got, want)):
+            # rounding differences of one call (split-K order) feed the next, so the comparison is against
+            # the scale of the output; a launch that ran ahead of its input would be off by O(1)
+            a32, b32 = a.float(), b.float()
+            assert torch.isfinite(a32).all(), (attempt, i)
+            assert (a32 - b32).abs().max().item() <= 0.03 * b32.abs().max().item(), (attempt, i, M)
+    assert sk._C.device_status() == 0
