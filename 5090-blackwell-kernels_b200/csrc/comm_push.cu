@@ -42,6 +42,10 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 
 __global__ void __launch_bounds__(kCommThreads) allreduce_push_kernel(const CommParams p) {
+    // Chained launch: the GEMM behind this kernel may start streaming its weights now; this kernel
+    // itself starts once the GEMM in front (whose output it sums) has completed.
+    pdl_release();
+    pdl_wait();
     unsigned char* local = p.bufs[p.rank];
     unsigned* seq_ptr = reinterpret_cast<unsigned*>(local + kCommSeqOffset);
     unsigned* done_ptr = seq_ptr + 1;
@@ -191,7 +195,6 @@ extern "C" int spk_allreduce_push_bf16(void* data, long long n, void* const* buf
     }
     p.data = static_cast<__nv_bfloat16*>(data);
     p.n = n, p.slot_elems = slot_elems, p.rank = rank, p.world = world;
-    allreduce_push_kernel<<<kCommCtas, kCommThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    SPK_CHECK_LAUNCH();
+    SPK_CUDA(launch_chained(allreduce_push_kernel, dim3(kCommCtas), dim3(kCommThreads), 0, static_cast<cudaStream_t>(stream), p));
     return SPK_OK;
 }

@@ -333,7 +333,7 @@ struct DecodeParams {
 };
 
 template <int NT, int MODE>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(192, 1)
 qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                          const DecodeParams p) {
     using Cfg = DecodeCfg<NT, MODE>;
@@ -485,13 +485,14 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 if (done + 1 == static_cast<unsigned>(p.split)) {
                     __threadfence();
                     if (n < p.N) {
-                        for (int m0 = 0; m0 < p.M; m0 += 16) {  // loads of a batch in flight together
-                            float w[16];
+                        constexpr int kBatch = NT < 32 ? NT : 32;  // loads in flight together: one round trip per batch
+                        for (int m0 = 0; m0 < p.M; m0 += kBatch) {
+                            float w[kBatch];
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
+                            for (int j = 0; j < kBatch; ++j)
                                 w[j] = m0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(m0 + j) * p.N + n) : 0.f;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
+                            for (int j = 0; j < kBatch; ++j)
                                 if (m0 + j < p.M) {
                                     p.C[static_cast<size_t>(m0 + j) * p.N + n] = __float2bfloat16_rn(w[j]);
                                     __stcg(p.partials + static_cast<size_t>(m0 + j) * p.N + n, 0.f);

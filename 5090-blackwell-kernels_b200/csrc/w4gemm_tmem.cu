@@ -377,15 +377,16 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 if (done + static_cast<unsigned>(pend_n[i]) == static_cast<unsigned>(chunks)) {
                     __threadfence();
                     const int n = pend_ss[i] * 128 + quarter * 32 + lane;
-                    for (int t0 = 0; t0 < p.M; t0 += 16) {  // all loads of a batch in flight together
-                        float v[16];
+                    constexpr int kBatch = NT < 32 ? NT : 32;  // loads in flight together: one round trip per batch
+                    for (int t0 = 0; t0 < p.M; t0 += kBatch) {
+                        float w[kBatch];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            v[j] = t0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n) : 0.f;
+                        for (int j = 0; j < kBatch; ++j)
+                            w[j] = t0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n) : 0.f;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
+                        for (int j = 0; j < kBatch; ++j)
                             if (t0 + j < p.M) {
-                                p.C[static_cast<size_t>(t0 + j) * p.N + n] = __float2bfloat16_rn(v[j]);
+                                p.C[static_cast<size_t>(t0 + j) * p.N + n] = __float2bfloat16_rn(w[j]);
                                 __stcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n, 0.f);
                             }
                     }
