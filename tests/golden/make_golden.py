@@ -148,7 +148,9 @@ def fp4_fixtures(ref) -> dict:
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of the reference repository>")
+    root = sys.argv[1]
     ref = load_reference(root)
     torch.set_num_threads(1)
     for name, fn in (("w4", w4_fixtures), ("fp8", fp8_fixtures), ("fp4", fp4_fixtures)):
