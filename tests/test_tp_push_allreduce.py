@@ -1,5 +1,5 @@
 """The push all-reduce on two GPUs of one node against an fp32 rank-order sum (bit for bit), eager
-and replayed from a CUDA graph. Needs two GPUs; skipped otherwise. The ranks are child processes."""
+and replayed from a CUDA graph, and its bounded wait when a peer does not take part. Needs two GPUs; skipped otherwise. The ranks are child processes."""
 
 import os
 import subprocess
@@ -55,6 +55,16 @@ for rep in range(4):
     for _ in range(world): s2 += s1.float()
     assert torch.equal(buf, s2.to(torch.bfloat16)), rep
 assert ar.status() == 0
+# a peer that never makes the call: the wait gives up after about a second and leaves a status word
+# (no trap, the context stays usable); the data is left unsummed
+dist.barrier()
+if rank == 0:
+    lone = torch.ones(8, device="cuda", dtype=torch.bfloat16)
+    ar(lone)
+    assert ar.status() == 3, "expected the bounded wait to report a timeout"
+    assert torch.equal(lone, torch.ones_like(lone))
+    assert torch.zeros(4, device="cuda").sum().item() == 0.0   # the device still answers
+dist.barrier()
 ar.close()
 dist.barrier()
 print("RANK_OK", rank, flush=True)
