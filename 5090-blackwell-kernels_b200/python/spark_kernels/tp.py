@@ -10,6 +10,7 @@ is strided in it, so slicing before `w4_repack` is the simple exact way.
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 
 import torch
@@ -133,26 +134,62 @@ class PushAllReduce:
         self._C, self.group, self.slot_elems = sk._C, group, int(max_elems)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.device = torch.device(device)
-        with torch.cuda.device(self.device):
-            self.local = self._C.comm_alloc(self.world, self.slot_elems)
+        # Every rank takes part in both exchanges even if a local step failed, so that a failure (CUDA IPC
+        # closed to the container, out of memory) raises on all ranks instead of leaving peers in a collective.
+        self.local, self.ptrs, handle, err = 0, [], None, None
+        with self._on_device():
+            try:
+                self.local = self._C.comm_alloc(self.world, self.slot_elems)
+                handle = self._C.comm_export(self.local)
+            except Exception as e:  # noqa: BLE001 - reported to every rank below
+                err = f"rank {self.rank}: {e}"
             handles = [None] * self.world
-            dist.all_gather_object(handles, self._C.comm_export(self.local), group=group)
-            self.ptrs = [self.local if r == self.rank else self._C.comm_open(handles[r]) for r in range(self.world)]
+            dist.all_gather_object(handles, (handle, err), group=group)
+            errs = [e for (_, e) in handles if e]
+            if not errs:
+                try:
+                    self.ptrs = [self.local if r == self.rank else self._C.comm_open(handles[r][0]) for r in range(self.world)]
+                except Exception as e:  # noqa: BLE001
+                    err = f"rank {self.rank}: {e}"
+            opened = [None] * self.world
+            dist.all_gather_object(opened, err, group=group)
+            errs = errs or [e for e in opened if e]
+            if errs:
+                self._release()
+                raise RuntimeError("push all-reduce unavailable: " + "; ".join(errs))
         dist.barrier(group)
+
+    def _on_device(self):
+        return torch.cuda.device(self.device) if self.device.type == "cuda" else contextlib.nullcontext()
+
+    def _release(self) -> None:
+        for ptr in self.ptrs:
+            if ptr and ptr != self.local:
+                try:
+                    self._C.comm_close(ptr)
+                except Exception:  # noqa: BLE001 - best effort on the failure path
+                    pass
+        if self.local:
+            try:
+                self._C.comm_free(self.local)
+            except Exception:  # noqa: BLE001
+                pass
+        self.local, self.ptrs = 0, []
 
     def __call__(self, t: torch.Tensor) -> torch.Tensor:
         return self._C.allreduce_push(t, self.ptrs, self.rank, self.slot_elems)
 
     def status(self) -> int:
         """0, or the status a bounded wait for a peer left behind (synchronizes the device)."""
-        with torch.cuda.device(self.device):
+        with self._on_device():
             return self._C.comm_status(self.local)
 
     def close(self) -> None:
         import torch.distributed as dist
 
-        with torch.cuda.device(self.device):
-            torch.cuda.synchronize()
+        with self._on_device():
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
             dist.barrier(self.group)  # nobody closes a buffer a peer may still be writing to
             for r, ptr in enumerate(self.ptrs):
                 if r != self.rank:

@@ -81,3 +81,78 @@ def test_column_indices_llama3_8b():
         assert tp.column_indices("qkv", s, 0, n).numel() % 16 == 0
     with pytest.raises(ValueError):
         tp.column_indices("down", s, 0, 2)
+
+
+class _FakeComm:
+    """Stands in for the library's spk_comm_* entry points on CPU: buffers are ints, handles are the
+    int as 64 bytes; rank `fail_export_on` cannot export, rank `fail_open_on` cannot open."""
+
+    def __init__(self, rank, fail_export_on=-1, fail_open_on=-1):
+        self.rank, self.fail_export_on, self.fail_open_on = rank, fail_export_on, fail_open_on
+        self.freed, self.closed, self.calls = [], [], []
+
+    def comm_alloc(self, world, slot_elems):
+        return 1000 + self.rank
+
+    def comm_export(self, ptr):
+        if self.rank == self.fail_export_on:
+            raise RuntimeError("ipc closed")
+        return ptr.to_bytes(64, "little")
+
+    def comm_open(self, handle):
+        if self.rank == self.fail_open_on:
+            raise RuntimeError("open refused")
+        return int.from_bytes(handle, "little") + 5000  # a peer mapping has another address
+
+    def comm_close(self, ptr):
+        self.closed.append(ptr)
+
+    def comm_free(self, ptr):
+        self.freed.append(ptr)
+
+    def comm_status(self, ptr):
+        return 0
+
+    def allreduce_push(self, t, ptrs, rank, slot_elems):
+        self.calls.append((tuple(ptrs), rank, slot_elems))
+        return t
+
+
+def _push_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from types import SimpleNamespace
+
+        from spark_kernels import tp
+
+        res = {}
+        fake = _FakeComm(rank)
+        ar = tp.PushAllReduce(SimpleNamespace(_C=fake), None, 4096, "cpu")
+        # own buffer at index rank, the peers' mappings elsewhere, in rank order
+        res["ptrs"] = ar.ptrs == [1000 + r if r == rank else 6000 + r for r in range(world)]
+        ar(torch.zeros(8))
+        res["call"] = fake.calls == [(tuple(ar.ptrs), rank, 4096)]
+        ar.close()
+        res["closed"] = fake.closed == [6000 + r for r in range(world) if r != rank] and fake.freed == [1000 + rank]
+        # a rank that cannot export / open: every rank raises, nobody is left in a collective, buffers are released
+        for kw in ({"fail_export_on": 1}, {"fail_open_on": 0}):
+            fake = _FakeComm(rank, **kw)
+            try:
+                tp.PushAllReduce(SimpleNamespace(_C=fake), None, 4096, "cpu")
+                res[str(kw)] = False
+            except RuntimeError as e:
+                res[str(kw)] = "push all-reduce unavailable" in str(e)
+        dist.barrier()
+        out[rank] = res
+    finally:
+        dist.destroy_process_group()
+
+
+def test_push_allreduce_setup_agrees_across_ranks():
+    world = 2
+    out = mp.Manager().dict()
+    mp.spawn(_push_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert len(out) == world
+    for rank in range(world):
+        assert all(out[rank].values()), (rank, dict(out[rank]))
