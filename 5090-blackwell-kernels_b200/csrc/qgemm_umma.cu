@@ -5,7 +5,7 @@
 //   kNvfp4   e2m1 x e2m1, e4m3 scale per 16 k            kind::mxf4nvf4.block_scale.scale_vec::4X
 //   kMxfp4   e2m1 x e2m1, ue8m0 scale per 32 k           kind::mxf4nvf4.block_scale.scale_vec::2X
 //
-// One CTA computes one 128 x BN tile of C. Roles, one warp each unless noted:
+// A persistent CTA computes 128 x BN tiles of C one after another. Roles, one warp each unless noted:
 //   warp 0   producer: per K block (128 bytes of K per row) one thread issues two tiled TMA loads
 //            (A 128 x 128 B, Bt BN x 128 B, 128-byte swizzle) and, in the block-scaled modes, bulk
 //            copies of the 512-byte scale tiles (128 rows x 4 scales, the blocked layout of the
@@ -145,12 +145,17 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kStages * Cfg::kStageBytes);
     uint64_t* empty = full + kStages;
-    uint64_t* acc_ready = empty + kStages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_ready = empty + kStages;  // MMA commit: the tile's accumulator is complete
+    uint64_t* acc_free = acc_ready + 1;     // the 4 epilogue warps have read it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
+    volatile uint32_t* mma_failed = tmem_slot + 1;  // set before the MMA warp releases the epilogue after a failed wait
 
+    // Persistent: CTA b computes tiles b, b + gridDim.x, ... (grouped order). The stage ring runs on
+    // across tiles, so the producer fills the next tile's first stages while the epilogue drains the
+    // accumulator, and set-up (barriers, TMEM, tensor maps) is paid once per CTA.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int tile_m, tile_n;
-    grouped_tile((p.M + kBM - 1) / kBM, (p.N + BN - 1) / BN, blockIdx.x, tile_m, tile_n);
+    const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
+    const int total_tiles = tiles_m * tiles_n;
     const int k_bytes = p.K / T::kElemsPerByte;
     const int k_blocks = (k_bytes + kBKBytes - 1) / kBKBytes;
 
@@ -160,6 +165,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_ready, 1);
+        mbar_init(acc_free, 4);
+        *mma_failed = 0u;
         ptx::fence_mbar_init();
         umma::prefetch_tensormap(&map_a);
         umma::prefetch_tensormap(&map_b);
@@ -171,91 +178,119 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t tmem_acc = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % kStages;
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            int tile_m, tile_n;
+            grouped_tile(tiles_m, tiles_n, tile, tile_m, tile_n);
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
                 // a fresh barrier passes a wait on the opposite parity, so the first lap does not block
-                if (!mbar_wait(&empty[s], ((kb / kStages) & 1) ^ 1, p.status)) break;
-                mbar_arrive_expect_tx(&full[s], Cfg::kTxBytes);
-                unsigned char* st = tiles + s * Cfg::kStageBytes;
-                umma::tma_load_2d(st, &map_a, kb * kBKBytes, tile_m * kBM, &full[s]);
-                umma::tma_load_2d(st + Cfg::kABytes, &map_b, kb * kBKBytes, tile_n * BN, &full[s]);
-                if (T::kScaled) {
-                    unsigned char* sf = st + Cfg::kABytes + Cfg::kBBytes;
-                    const size_t tile0 = static_cast<size_t>(kb) * T::kTiles;
-                    bulk_g2s(sf, p.sfa + (static_cast<size_t>(tile_m) * p.sf_tiles_per_rowblock + tile0) * kSfTile,
-                             Cfg::kSfABytes, &full[s]);
+                ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, p.status));
+                if (!ok) break;
+                if (umma::elect_one()) {
+                    mbar_arrive_expect_tx(&full[s], Cfg::kTxBytes);
+                    unsigned char* st = tiles + s * Cfg::kStageBytes;
+                    umma::tma_load_2d(st, &map_a, kb * kBKBytes, tile_m * kBM, &full[s]);
+                    umma::tma_load_2d(st + Cfg::kABytes, &map_b, kb * kBKBytes, tile_n * BN, &full[s]);
+                    if (T::kScaled) {
+                        unsigned char* sf = st + Cfg::kABytes + Cfg::kBBytes;
+                        const size_t tile0 = static_cast<size_t>(kb) * T::kTiles;
+                        bulk_g2s(sf, p.sfa + (static_cast<size_t>(tile_m) * p.sf_tiles_per_rowblock + tile0) * kSfTile,
+                                 Cfg::kSfABytes, &full[s]);
 #pragma unroll
-                    for (int i = 0; i < NB; ++i)
-                        bulk_g2s(sf + Cfg::kSfABytes + i * (T::kTiles * kSfTile),
-                                 p.sfb + (static_cast<size_t>(tile_n * NB + i) * p.sf_tiles_per_rowblock + tile0) * kSfTile,
-                                 T::kTiles * kSfTile, &full[s]);
+                        for (int i = 0; i < NB; ++i)
+                            bulk_g2s(sf + Cfg::kSfABytes + i * (T::kTiles * kSfTile),
+                                     p.sfb + (static_cast<size_t>(tile_n * NB + i) * p.sf_tiles_per_rowblock + tile0) * kSfTile,
+                                     T::kTiles * kSfTile, &full[s]);
+                    }
                 }
+                __syncwarp();
+                if (++s == kStages) s = 0, ph ^= 1u;
             }
         }
     } else if (warp == 1) {
         // The loop runs warp-wide so that stage indices and descriptors stay uniform; one elected lane
         // issues the tcgen05 instructions (always the same lane, so its commits cover its MMAs).
-        {
-            bool ok = true;
-            int s = 0;
-            unsigned ph = 0;
+        bool ok = true;
+        int s = 0, it = 0;
+        unsigned ph = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            // the epilogue must have read the previous tile's accumulator
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_free, (it & 1) ^ 1, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, p.status));
                 if (!ok) break;
                 umma::fence_after_sync();
                 if (umma::elect_one()) {
-                const unsigned char* st = tiles + s * Cfg::kStageBytes;
-                const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + Cfg::kABytes);
-                if (!T::kScaled) {
-                    constexpr uint32_t idesc = umma::instr_desc(kBM, BN, 0, 0);  // e4m3 x e4m3 -> f32
+                    const unsigned char* st = tiles + s * Cfg::kStageBytes;
+                    const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + Cfg::kABytes);
+                    if (!T::kScaled) {
+                        constexpr uint32_t idesc = umma::instr_desc(kBM, BN, 0, 0);  // e4m3 x e4m3 -> f32
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma::mma_f8f6f4(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
-                                         kb > 0 || k > 0);
-                } else {
-                    // this stage's scale tiles, shared -> TMEM: A tile t at columns sfa + 4 t; Bt row block i of
-                    // tile t at sfb + 4 (NB t + i), so the NB row blocks of one MMA sit side by side
-                    const unsigned char* sf = st + Cfg::kABytes + Cfg::kBBytes;
-                    const uint32_t sfa_col = tmem_acc + Cfg::kSfColBase + s * kSfColsPerStage, sfb_col = sfa_col + 16;
+                        for (int k = 0; k < 4; ++k)
+                            umma::mma_f8f6f4(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
+                                             kb > 0 || k > 0);
+                    } else {
+                        // this stage's scale tiles, shared -> TMEM: A tile t at columns sfa + 4 t; Bt row block i of
+                        // tile t at sfb + 4 (NB t + i), so the NB row blocks of one MMA sit side by side
+                        const unsigned char* sf = st + Cfg::kABytes + Cfg::kBBytes;
+                        const uint32_t sfa_col = tmem_acc + Cfg::kSfColBase + s * kSfColsPerStage, sfb_col = sfa_col + 16;
 #pragma unroll
-                    for (int t = 0; t < T::kTiles; ++t) {
-                        tmem_cp_sf(sfa_col + 4 * t, sf_desc(sf + t * kSfTile));
+                        for (int t = 0; t < T::kTiles; ++t) {
+                            tmem_cp_sf(sfa_col + 4 * t, sf_desc(sf + t * kSfTile));
 #pragma unroll
-                        for (int i = 0; i < NB; ++i)
-                            tmem_cp_sf(sfb_col + 4 * (NB * t + i), sf_desc(sf + Cfg::kSfABytes + (i * T::kTiles + t) * kSfTile));
+                            for (int i = 0; i < NB; ++i)
+                                tmem_cp_sf(sfb_col + 4 * (NB * t + i), sf_desc(sf + Cfg::kSfABytes + (i * T::kTiles + t) * kSfTile));
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            // which scale tile and which bytes of its 32-bit words MMA k uses
+                            const int t = MODE == kNvfp4 ? k : MODE == kMxfp4 ? (k >> 1) : 0;
+                            const int sf_id = MODE == kNvfp4 ? 0 : MODE == kMxfp4 ? 2 * (k & 1) : k;
+                            const uint32_t idesc = instr_desc_scaled(kBM, BN, MODE == kFp8Mx ? 0 : 1, MODE == kNvfp4 ? 0 : 1, sf_id);
+                            mma_scaled<MODE>(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
+                                             sfa_col + 4 * t, sfb_col + 4 * NB * t, kb > 0 || k > 0);
+                        }
                     }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        // which scale tile and which bytes of its 32-bit words MMA k uses
-                        const int t = MODE == kNvfp4 ? k : MODE == kMxfp4 ? (k >> 1) : 0;
-                        const int sf_id = MODE == kNvfp4 ? 0 : MODE == kMxfp4 ? 2 * (k & 1) : k;
-                        const uint32_t idesc = instr_desc_scaled(kBM, BN, MODE == kFp8Mx ? 0 : 1, MODE == kNvfp4 ? 0 : 1, sf_id);
-                        mma_scaled<MODE>(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
-                                         sfa_col + 4 * t, sfb_col + 4 * NB * t, kb > 0 || k > 0);
-                    }
-                }
-                umma::mma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                    umma::mma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                    if (kb == k_blocks - 1) umma::mma_commit(acc_ready);  // the tile's accumulator is complete
                 }
                 __syncwarp();
                 if (++s == kStages) s = 0, ph ^= 1u;
             }
-            if (umma::elect_one()) umma::mma_commit(acc_ready);  // fires after every MMA above has completed (also on failure)
-            __syncwarp();
         }
+        if (!ok) {  // release the epilogue on a failed wait
+            *mma_failed = 1u;
+            __threadfence_block();
+            if (umma::elect_one()) umma::mma_commit(acc_ready);
+        }
+        __syncwarp();
     } else {
         // ---- epilogue: warps 2..5 -> TMEM lane quarters 2, 3, 0, 1 ----
         const int quarter = warp & 3;
-        const bool ok = mbar_wait(acc_ready, 0, p.status);
-        umma::fence_after_sync();
-        if (ok) {
-            const float s = (p.scale_a ? *p.scale_a : 1.0f) * (p.scale_b ? *p.scale_b : 1.0f);
+        const float s = (p.scale_a ? *p.scale_a : 1.0f) * (p.scale_b ? *p.scale_b : 1.0f);
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            int tile_m, tile_n;
+            grouped_tile(tiles_m, tiles_n, tile, tile_m, tile_n);
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, it & 1, p.status)) && *mma_failed == 0u;
+            umma::fence_after_sync();
+            if (!ok) break;
             const int row = tile_m * kBM + quarter * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 umma::tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, r);
                 umma::tmem_ld_wait();
+                if (c0 + 32 == BN) {  // every column has been read: the next tile may overwrite the accumulator
+                    umma::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_free);
+                }
                 const int col = tile_n * BN + c0;
                 if (row < p.M && col < p.N) {  // N % 64 == 0 and c0 % 32 == 0: a 32-column run is all in or all out
                     uint4 out[4];
@@ -301,7 +336,7 @@ int launch_umma(const simt::Params& q, const unsigned char* sfa, const unsigned 
     p.sfa = sfa, p.sfb = sfb;
     p.sf_tiles_per_rowblock = MODE == kNvfp4 ? q.K / 64 : q.K / 128;
     p.status = dev->status;
-    const int grid = cdiv(q.M, kBM) * cdiv(q.N, BN);
+    const int grid = std::min(cdiv(q.M, kBM) * cdiv(q.N, BN), dev->sm_count * Cfg::kCtasPerSm);
     kernel<<<grid, 192, Cfg::kSmem, stream>>>(map_a, map_b, p);
     SPK_CHECK_LAUNCH();
     return SPK_OK;
