@@ -100,6 +100,11 @@ __device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Four fp32 additions to consecutive, 16-byte-aligned words of global memory in one reduction.
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // D[tmem] (+)= A[tmem] * B[smem], bf16 operands, K = 16.
 __device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool accumulate) {
     asm volatile(
@@ -348,14 +353,20 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(&acc_free[buf]);
             const int n = ss * 128 + quarter * 32 + lane;  // TMEM lane = column of the super-strip
             const bool whole_k = seg_ch0 == 0 && ch == chunks - 1;
+            if (whole_k) {
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                if (t < p.M) {
-                    if (whole_k)
-                        p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[t]));
-                    else
-                        atomicAdd(p.partials + static_cast<size_t>(t) * p.N + n, __uint_as_float(v[t]));
-                }
+                for (int t = 0; t < NT; ++t)
+                    if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[t]));
+            } else {
+                // The scratch of this kernel is [32-column block][NT / 4][lane][4 tokens]: a lane's partial sums go
+                // out as NT / 4 vector reductions and a warp's reduction covers 512 contiguous bytes (a scalar
+                // reduction per token row cost ~100 cycles each here).
+                float* mine = p.partials + (static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane) * 4;
+#pragma unroll
+                for (int t = 0; t < NT; t += 4)
+                    if (t < p.M)
+                        red_add_v4(mine + t * 32, __uint_as_float(v[t]), __uint_as_float(v[t + 1]), __uint_as_float(v[t + 2]),
+                                   __uint_as_float(v[t + 3]));
             }
             if (!whole_k) {
                 pend_ss[n_pend] = ss;
@@ -377,18 +388,20 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 if (done + static_cast<unsigned>(pend_n[i]) == static_cast<unsigned>(chunks)) {
                     __threadfence();
                     const int n = pend_ss[i] * 128 + quarter * 32 + lane;
-                    constexpr int kBatch = NT < 32 ? NT : 32;  // loads in flight together: one round trip per batch
-                    for (int t0 = 0; t0 < p.M; t0 += kBatch) {
-                        float w[kBatch];
+                    // this lane's NT sums: NT / 4 vector loads in one round trip, re-zero, store bf16
+                    float4* mine = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane;
+                    float4 w[NT / 4];
 #pragma unroll
-                        for (int j = 0; j < kBatch; ++j)
-                            w[j] = t0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n) : 0.f;
+                    for (int j = 0; j < NT / 4; ++j) w[j] = 4 * j < p.M ? __ldcg(mine + j * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                        for (int j = 0; j < kBatch; ++j)
-                            if (t0 + j < p.M) {
-                                p.C[static_cast<size_t>(t0 + j) * p.N + n] = __float2bfloat16_rn(w[j]);
-                                __stcg(p.partials + static_cast<size_t>(t0 + j) * p.N + n, 0.f);
-                            }
+                    for (int j = 0; j < NT / 4; ++j)
+                        if (4 * j < p.M) __stcg(mine + j * 32, make_float4(0.f, 0.f, 0.f, 0.f));
+#pragma unroll
+                    for (int j = 0; j < NT / 4; ++j) {
+                        const float e[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (4 * j + q < p.M) p.C[static_cast<size_t>(4 * j + q) * p.N + n] = __float2bfloat16_rn(e[q]);
                     }
                     if (lane == 0) *counter = 0u;
                 }
@@ -461,7 +474,7 @@ int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, co
     }();
     if (!enabled || M < min_m || N % 128 != 0 || (K / w4::kGroup) % kChunkGroups != 0) return SPK_OK;
     if (M == 16 && min_m == 16 && static_cast<int64_t>(K) * N < (int64_t{1} << 25)) return SPK_OK;
-    if (static_cast<int64_t>(std::min(M, 64)) * N > kPartialFloats || (N / 128) * 4 > kCounters) return SPK_OK;
+    if (static_cast<int64_t>(64) * N > kPartialFloats || (N / 128) * 4 > kCounters) return SPK_OK;  // scratch is [N][NT]
     if (reinterpret_cast<uintptr_t>(A) % 16 != 0 || static_cast<int64_t>(std::min(M, 64)) * K * 2 > kActScratchBytes) return SPK_OK;
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;
