@@ -519,11 +519,16 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                         if (m < p.M) p.C[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[m]) * s);
                 }
             } else {
-                if (n < p.N) {
+                // Split-K scratch laid out [32-column block][NT / 4][lane][4 tokens]: NT / 4 vector reductions per
+                // lane, each warp-wide reduction 512 contiguous bytes (rows past M are exact zeros).
+                float* mine = p.partials + (static_cast<size_t>(tile_n * 4 + quarter) * (NT / 4) * 32 + lane) * 4;
 #pragma unroll
-                    for (int m = 0; m < NT; ++m)
-                        if (m < p.M) atomicAdd(p.partials + static_cast<size_t>(m) * p.N + n, __uint_as_float(v[m]) * s);
-                }
+                for (int m = 0; m < NT; m += 4)
+                    if (m < p.M)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mine + m * 32), "f"(__uint_as_float(v[m]) * s),
+                                     "f"(__uint_as_float(v[m + 1]) * s), "f"(__uint_as_float(v[m + 2]) * s),
+                                     "f"(__uint_as_float(v[m + 3]) * s)
+                                     : "memory");
                 __threadfence();
                 __syncwarp();
                 unsigned done = 0;
@@ -532,19 +537,20 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 done = __shfl_sync(0xffffffffu, done, 0);
                 if (done + 1 == static_cast<unsigned>(p.split)) {
                     __threadfence();
+                    float4* all = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(tile_n * 4 + quarter) * (NT / 4) * 32 + lane;
+                    float4 w[NT / 4];
+#pragma unroll
+                    for (int j = 0; j < NT / 4; ++j) w[j] = 4 * j < p.M ? __ldcg(all + j * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < NT / 4; ++j)
+                        if (4 * j < p.M) __stcg(all + j * 32, make_float4(0.f, 0.f, 0.f, 0.f));
                     if (n < p.N) {
-                        constexpr int kBatch = NT < 32 ? NT : 32;  // loads in flight together: one round trip per batch
-                        for (int m0 = 0; m0 < p.M; m0 += kBatch) {
-                            float w[kBatch];
 #pragma unroll
-                            for (int j = 0; j < kBatch; ++j)
-                                w[j] = m0 + j < p.M ? __ldcg(p.partials + static_cast<size_t>(m0 + j) * p.N + n) : 0.f;
+                        for (int j = 0; j < NT / 4; ++j) {
+                            const float e[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
 #pragma unroll
-                            for (int j = 0; j < kBatch; ++j)
-                                if (m0 + j < p.M) {
-                                    p.C[static_cast<size_t>(m0 + j) * p.N + n] = __float2bfloat16_rn(w[j]);
-                                    __stcg(p.partials + static_cast<size_t>(m0 + j) * p.N + n, 0.f);
-                                }
+                            for (int q = 0; q < 4; ++q)
+                                if (4 * j + q < p.M) p.C[static_cast<size_t>(4 * j + q) * p.N + n] = __float2bfloat16_rn(e[q]);
                         }
                     }
                     if (lane == 0) *counter = 0u;
@@ -604,7 +610,8 @@ int launch_decode_nt(const simt::Params& q, const unsigned char* sfw, const unsi
 }
 
 bool decode_fits(const simt::Params& p, size_t scratch_bytes_before) {
-    return static_cast<int64_t>(p.M) * p.N + static_cast<int64_t>(scratch_bytes_before / 4) <= kPartialFloats &&
+    // split-K scratch: 128 columns x up to 64 token slots per tile
+    return static_cast<int64_t>(cdiv(p.N, kBM)) * 128 * 64 + static_cast<int64_t>(scratch_bytes_before / 4) <= kPartialFloats &&
            cdiv(p.N, kBM) * 4 <= kCounters;
 }
 
