@@ -42,6 +42,7 @@ MS = (1, 16, 64)
 LAYERS = 16
 WORKLOAD = "llama3_8b_mlp_int4_decode"
 FALLBACK_HBM_GBS = 6650.0
+PUSH_MAX_BYTES = 128 << 10  # all-reduce payloads up to this size go by peer stores
 
 
 def alg_bytes(M: int, N: int, K: int) -> int:
@@ -197,7 +198,15 @@ def run_ours(args) -> None:
                 from spark_kernels import tp as tpmod_
 
                 pusher = tpmod_.PushAllReduce(sk, None, 64 * HIDDEN, dev)
-                reduce, reduce_name = pusher, "push (peer stores over NVLink, one kernel per rank)"
+                # one hop of peer stores wins while the sum is latency bound; from 256 KiB up every rank
+                # would push world x the tensor, and NCCL's in-switch reduction is faster (measured at tp8:
+                # 8 KiB 13.6 us per GEMM+sum against 19.6, 128 KiB 21.4 against 24.4, 512 KiB 36.8 against 29.2)
+                push_max = PUSH_MAX_BYTES
+
+                def reduce(t, _p=pusher):
+                    return _p(t) if t.numel() * t.element_size() <= push_max else dist.all_reduce(t)
+
+                reduce_name = f"push up to {push_max >> 10} KiB (peer stores over NVLink, one kernel per rank), nccl above"
             except Exception as e:  # CUDA IPC can be closed to a container; NCCL then carries the sum
                 reduce_name = f"nccl (push unavailable: {type(e).__name__})"
             ok_all = torch.tensor([1.0 if reduce_name.startswith("push") else 0.0], device=dev)
