@@ -886,12 +886,251 @@ int fp4gemm_umma_try(const simt::Params& p, int format, cudaStream_t stream, boo
                           : launch_umma<128, kMxfp4>(p, p.sfa, p.sfb, dev, stream);
 }
 
+// ---- fp32-block-scaled fp8 at decode shapes (M <= 64) -----------------------------------------------
+//
+// The decode arrangement (weights as the 128-row operand, K split over the SMs) with the per-block
+// fold of the block-scaled kernel: one TMA stage is one 128-k block, its four MMAs overwrite one of
+// two TMEM buffers, and the epilogue warps fold it into NT fp32 registers per thread,
+// acc[m] += block[n][m] * sA[m][kb] * sB[n / 128][kb] (the tile is one 128-row block of Bt, so sB is
+// one value per stage). The partial sums of the K slices then go through the scratch as above.
+struct DecodeBlkParams {
+    __nv_bfloat16* C;
+    int M, N, K;
+    const float* sA;  // [M][K / 128]
+    const float* sB;  // [cdiv(N, 128)][K / 128]
+    int n_tiles, split;
+    float* partials;
+    unsigned* counters;
+    int* status;
+};
+
+template <int NT>
+struct DecodeBlkCfg {
+    static constexpr int kStageBytes = (kBM + NT) * kBKBytes;  // multiples of 1024 for NT = 16, 32, 64
+    static constexpr int kSmem = kDecodeStages * kStageBytes + 1024 + 256;
+    static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(192, 1)
+qgemm_umma_decode_block128_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                                  const DecodeBlkParams p) {
+    using Cfg = DecodeBlkCfg<NT>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kDecodeStages * Cfg::kStageBytes);
+    uint64_t* empty = full + kDecodeStages;
+    uint64_t* tfull = empty + kDecodeStages;  // [2]
+    uint64_t* tfree = tfull + 2;              // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfree + 2);
+
+    pdl_release();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x % p.n_tiles, sk = blockIdx.x / p.n_tiles;
+    const int KB = p.K / 128;
+    const int kb0 = static_cast<int>(static_cast<long long>(sk) * KB / p.split);
+    const int kb1 = static_cast<int>(static_cast<long long>(sk + 1) * KB / p.split);
+
+    if (threadIdx.x < 2 * kDecodeStages) mbar_init(&full[threadIdx.x], 1);  // full[] and empty[] are contiguous
+    if (threadIdx.x >= 32 && threadIdx.x < 34) {
+        mbar_init(&tfull[threadIdx.x - 32], 1);
+        mbar_init(&tfree[threadIdx.x - 32], 4);
+    }
+    if (threadIdx.x == 64) {
+        umma::prefetch_tensormap(&map_w);
+        umma::prefetch_tensormap(&map_x);
+    }
+    ptx::fence_mbar_init();
+    if (warp == 1) umma::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    if (warp == 0) {
+        // weights first (the launch is chained), tokens after the kernel in front has completed
+        auto load_weights = [&](int kb, int s) {
+            mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+            umma::tma_load_2d(tiles + s * Cfg::kStageBytes, &map_w, kb * kBKBytes, tile_n * kBM, &full[s]);
+        };
+        auto load_tokens = [&](int kb, int s) {
+            umma::tma_load_2d(tiles + s * Cfg::kStageBytes + kBM * kBKBytes, &map_x, kb * kBKBytes, 0, &full[s]);
+        };
+        const int early = kb1 - kb0 < kDecodeStages ? kb1 - kb0 : kDecodeStages;
+        if (umma::elect_one())
+            for (int i = 0; i < early; ++i) load_weights(kb0 + i, i);
+        __syncwarp();
+        pdl_wait();
+        if (umma::elect_one())
+            for (int i = 0; i < early; ++i) load_tokens(kb0 + i, i);
+        __syncwarp();
+        int s = early == kDecodeStages ? 0 : early;
+        unsigned ph = early == kDecodeStages ? 1u : 0u;
+        bool ok = true;
+        for (int kb = kb0 + early; kb < kb1 && ok; ++kb) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, p.status));
+            if (!ok) break;
+            if (umma::elect_one()) {
+                load_weights(kb, s);
+                load_tokens(kb, s);
+            }
+            __syncwarp();
+            if (++s == kDecodeStages) s = 0, ph ^= 1u;
+        }
+    } else if (warp == 1) {
+        constexpr uint32_t idesc = umma::instr_desc(kBM, NT, 0, 0);  // e4m3 x e4m3 -> f32
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            const int i = kb - kb0, buf = i & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, p.status) && mbar_wait(&tfree[buf], ((i >> 1) & 1) ^ 1, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
+            if (umma::elect_one()) {
+                const unsigned char* st = tiles + s * Cfg::kStageBytes;
+                const uint64_t wdesc = umma::smem_desc_k128(st), xdesc = umma::smem_desc_k128(st + kBM * kBKBytes);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma::mma_f8f6f4(tmem_acc + buf * NT, umma::desc_advance(wdesc, 32 * k), umma::desc_advance(xdesc, 32 * k), idesc, k > 0);
+                umma::mma_commit(&empty[s]);
+                umma::mma_commit(&tfull[buf]);
+            }
+            __syncwarp();
+            if (++s == kDecodeStages) s = 0, ph ^= 1u;
+        }
+    } else {
+        // ---- epilogue warps: lane = weight row n of the tile; fold every block with its scales ----
+        const int quarter = warp & 3;
+        pdl_wait();
+        const int n = tile_n * kBM + quarter * 32 + lane;
+        const float* sb_row = p.sB + static_cast<size_t>(tile_n) * KB;
+        float acc[NT];
+#pragma unroll
+        for (int m = 0; m < NT; ++m) acc[m] = 0.f;
+        bool ok = true;
+        // Lane l fetches the block scales of tokens l and l + 32 one block ahead (two loads per lane and
+        // block instead of NT broadcast loads); the fold gets token m's scale by shuffle.
+        constexpr int kPer = NT > 32 ? 2 : 1;
+        auto fetch = [&](int kb, float (&out)[kPer]) {
+            const float fb = kb < kb1 ? __ldg(sb_row + kb) : 0.f;
+#pragma unroll
+            for (int h = 0; h < kPer; ++h) {
+                const int m = lane + 32 * h;
+                out[h] = (kb < kb1 && m < p.M) ? __ldg(p.sA + static_cast<size_t>(m) * KB + kb) * fb : 0.f;
+            }
+        };
+        float nxt[kPer];
+        fetch(kb0, nxt);
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            const int i = kb - kb0, buf = i & 1;
+            float cur[kPer];
+#pragma unroll
+            for (int h = 0; h < kPer; ++h) cur[h] = nxt[h];
+            fetch(kb + 1, nxt);
+            float fa[NT];
+#pragma unroll
+            for (int m = 0; m < NT; ++m) fa[m] = __shfl_sync(0xffffffffu, cur[m >> 5], m & 31);
+            ok = __all_sync(0xffffffffu, mbar_wait(&tfull[buf], (i >> 1) & 1, p.status));
+            if (!ok) break;
+            umma::fence_after_sync();
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                uint32_t r[16];
+                umma::tmem_ld_32x16(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + buf * NT + c0, r);
+                umma::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c0 + j] = fmaf(__uint_as_float(r[j]), fa[c0 + j], acc[c0 + j]);
+            }
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tfree[buf]);
+        }
+        if (ok && kb1 > kb0) {
+            if (p.split == 1) {
+                if (n < p.N) {
+#pragma unroll
+                    for (int m = 0; m < NT; ++m)
+                        if (m < p.M) p.C[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(acc[m]);
+                }
+            } else {
+                float* mine = p.partials + (static_cast<size_t>(tile_n * 4 + quarter) * (NT / 4) * 32 + lane) * 4;
+#pragma unroll
+                for (int m = 0; m < NT; m += 4)
+                    if (m < p.M)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mine + m * 32), "f"(acc[m]), "f"(acc[m + 1]),
+                                     "f"(acc[m + 2]), "f"(acc[m + 3])
+                                     : "memory");
+                __threadfence();
+                __syncwarp();
+                unsigned done = 0;
+                unsigned* counter = p.counters + tile_n * 4 + quarter;
+                if (lane == 0) done = atomicAdd(counter, 1u);
+                done = __shfl_sync(0xffffffffu, done, 0);
+                if (done + 1 == static_cast<unsigned>(p.split)) {
+                    __threadfence();
+                    float4* all = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(tile_n * 4 + quarter) * (NT / 4) * 32 + lane;
+                    float4 w[NT / 4];
+#pragma unroll
+                    for (int j = 0; j < NT / 4; ++j) w[j] = 4 * j < p.M ? __ldcg(all + j * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < NT / 4; ++j)
+                        if (4 * j < p.M) __stcg(all + j * 32, make_float4(0.f, 0.f, 0.f, 0.f));
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < NT / 4; ++j) {
+                            const float e[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                if (4 * j + q < p.M) p.C[static_cast<size_t>(4 * j + q) * p.N + n] = __float2bfloat16_rn(e[q]);
+                        }
+                    }
+                    if (lane == 0) *counter = 0u;
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) umma::tmem_dealloc(tmem_acc, Cfg::kTmemCols);
+}
+
+template <int NT>
+int launch_decode_block128(const simt::Params& q, DeviceState* dev, cudaStream_t stream) {
+    using Cfg = DecodeBlkCfg<NT>;
+    static_assert(Cfg::kStageBytes % 1024 == 0 && Cfg::kSmem <= 227 * 1024, "stage ring");
+    CUtensorMap map_w, map_x;
+    if (!umma::make_map_2d_u8(&map_w, q.Bt, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), kBM) ||
+        !umma::make_map_2d_u8(&map_x, q.A, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M), NT))
+        return fail(SPK_CUDA_ERROR, "fp8gemm_block128: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
+    auto kernel = qgemm_umma_decode_block128_kernel<NT>;
+    static bool configured[16] = {};
+    if (!configured[dev->device & 15]) {
+        SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        configured[dev->device & 15] = true;
+    }
+    DecodeBlkParams p{};
+    p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
+    p.sA = q.blk_a, p.sB = q.blk_b;
+    p.n_tiles = cdiv(q.N, kBM);
+    p.split = std::max(1, std::min(dev->sm_count / p.n_tiles, (q.K / 128) / 2));
+    p.partials = dev->partials, p.counters = dev->counters, p.status = dev->status;
+    SPK_CUDA(launch_chained(kernel, dim3(p.n_tiles * p.split), dim3(192), Cfg::kSmem, stream, map_w, map_x, p));
+    return SPK_OK;
+}
+
 // The fp32-block-scaled fp8 GEMM on the tensor cores (every shape; C rows must be 16-byte aligned).
 int fp8gemm_block128_umma_try(const simt::Params& q, cudaStream_t stream, bool* taken) {
     *taken = false;
     if (umma_disabled() || !aligned16(q.C)) return SPK_OK;
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;
+    if (q.M <= 64 && decode_fits(q, 0)) {  // decode: weights as the 128-row operand, K split over the SMs
+        *taken = true;
+        return q.M <= 16 ? launch_decode_block128<16>(q, dev, stream)
+               : q.M <= 32 ? launch_decode_block128<32>(q, dev, stream)
+                           : launch_decode_block128<64>(q, dev, stream);
+    }
     *taken = true;
     // 128 x 256 tiles (8 folding warps) once they fill the SMs; 128 x 128 for small problems
     const bool wide = q.N % 256 == 0 && static_cast<long long>(cdiv(q.M, kBM)) * (q.N / 256) >= dev->sm_count;
