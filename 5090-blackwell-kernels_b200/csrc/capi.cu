@@ -1,13 +1,13 @@
 // Library-wide pieces of the C-ABI: the error message, per-device state, init and status.
 #include <mutex>
 
+#include "ptx_sm100.cuh"
 #include "spk_common.cuh"
 
 namespace spk {
 
 namespace {
 thread_local char g_error[512] = "";
-constexpr int kMaxDevices = 16;
 DeviceState g_devices[kMaxDevices];
 std::mutex g_mutex;
 }  // namespace
@@ -77,7 +77,48 @@ extern "C" int spk_device_status(void* stream, int* code) {
     int host = 0;
     SPK_CUDA(cudaMemcpyAsync(&host, d->status, sizeof(int), cudaMemcpyDeviceToHost, st));
     SPK_CUDA(cudaStreamSynchronize(st));
-    if (host != 0) SPK_CUDA(cudaMemsetAsync(d->status, 0, sizeof(int), st));
+    if (host != 0) {
+        // A kernel that gave up on a wait returned without its completion step: partial sums and strip
+        // counters may be left behind, and every later split-K launch assumes they are zero. Put the
+        // scratch back into its clean state together with the status word.
+        SPK_CUDA(cudaMemsetAsync(d->partials, 0, kPartialFloats * sizeof(float), st));
+        SPK_CUDA(cudaMemsetAsync(d->counters, 0, kCounters * sizeof(unsigned), st));
+        SPK_CUDA(cudaMemsetAsync(d->status, 0, sizeof(int), st));
+    }
     *code = host;
+    return SPK_OK;
+}
+
+// ---- a wait that runs out, for tests -------------------------------------------------------------
+namespace spk {
+namespace {
+// One thread waits (a few thousand polls, microseconds) for a barrier phase that nothing completes,
+// exactly as a broken pipeline would make a kernel of this library wait, records SPK_TIMEOUT in the
+// status word and returns. Before that it leaves `dirty` floats and counters non-zero, which is the
+// state an interrupted split-K kernel leaves behind.
+__global__ void expire_wait_kernel(float* partials, unsigned* counters, int dirty, int* status) {
+    __shared__ uint64_t bar;
+    for (int i = threadIdx.x; i < dirty; i += blockDim.x) {
+        partials[i] = 1.0f;
+        counters[i] = 1u;
+    }
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_mbar_init();
+        bool done = false;
+        for (int i = 0; i < 4096 && !done; ++i) done = ptx::mbar_try_wait(&bar, 0);
+        if (!done) atomicCAS(status, 0, SPK_TIMEOUT);
+    }
+}
+}  // namespace
+}  // namespace spk
+
+extern "C" int spk_debug_expire_wait(int dirty, void* stream) {
+    using namespace spk;
+    SPK_REQUIRE(dirty >= 0 && dirty <= kCounters, "spk_debug_expire_wait: dirty must be in [0, %d]", kCounters);
+    DeviceState* d = nullptr;
+    if (int rc = device_state(&d)) return rc;
+    expire_wait_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(d->partials, d->counters, dirty, d->status);
+    SPK_CHECK_LAUNCH();
     return SPK_OK;
 }

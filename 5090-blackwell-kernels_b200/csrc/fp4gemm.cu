@@ -1,8 +1,9 @@
 // fp4 (e2m1) GEMM, NVFP4 and MXFP4: C = scale_a * scale_b * sum_k (sfa A)(sfb Bt), operands packed
 // two to a byte, block scales in the blocked layout, bf16 out, fp32 accumulation.
 // Contract: reference include/spark/kernels.h:296-331.
-//   0  CUDA-core kernel, M % 16 == 0     1  CUDA-core kernel, any M
-//   2  tensor-core kernel, M and N multiples of 128 and at least one 128 x 128 tile per SM
+//   0  CUDA-core kernel, M % 16 == 0
+//   1  any M: tcgen05 tiles above 64 tokens (ragged M by TMA zero fill), tcgen05 split-K decode below
+//   2  the same tile kernel under the reference's shape rule (M, N multiples of 128, a tile per SM)
 #include "qgemm_simt.cuh"
 
 namespace spk {
@@ -56,7 +57,7 @@ extern "C" int spk_fp4gemm(const void* A, const void* Bt, void* C, int M, int N,
     p.M = M, p.N = N, p.K = K;
     p.scale_a = scale_a, p.scale_b = scale_b;
     p.sfa = sfa, p.sfb = sfb;
-    if (variant == 2 || (variant == 1 && M <= 64)) {  // tensor-core routes: large tiles, and decode with split-K
+    if (variant >= 1) {  // tensor cores for every M: 128-row tiles above 64 tokens, split-K decode below
         bool taken = false;
         const int rc = fp4gemm_umma_try(p, format, stream, &taken);
         if (taken || rc != SPK_OK) return rc;

@@ -13,6 +13,7 @@
 namespace spk {
 // defined in fp8gemm_umma.cu
 int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t stream, bool* taken);
+const char* fp8gemm_umma_plan(int M, int N, int K, bool mx, int variant, bool c_aligned, int sms);
 int fp8gemm_block128_umma_try(const simt::Params& p, cudaStream_t stream, bool* taken);
 namespace {
 
@@ -46,8 +47,17 @@ bool supports(int M, int N, int K, int variant, bool mx) {
     return true;
 }
 
+// The variant that really runs. Variant 3 under the legacy route (-2, reference include/spark/kernels.h:281-294:
+// "the old route") is what this library's ladder had before the per-shape rule: variant 2 where its
+// tile rule holds, else the CUDA-core kernel.
+int effective_variant(int M, int N, int K, int variant) {
+    if (variant != 3 || g_v3_route != -2) return variant;
+    return tensor_core_shape(M, N, K, sm_count_or(148)) ? 2 : 1;
+}
+
 int run(const simt::Params& p, bool mx, int variant, cudaStream_t stream) {
-    // The tensor-core route (variants 2 and 3) is added by fp8gemm_umma.cu through this hook.
+    variant = effective_variant(p.M, p.N, p.K, variant);
+    // The tensor-core route (variants 2 and 3) lives in qgemm_umma.cu and is reached through this hook.
     if (variant == 2 || variant == 3) {
         bool taken = false;
         const int rc = fp8gemm_umma_try(p, mx, variant, stream, &taken);
@@ -128,16 +138,20 @@ extern "C" int spk_fp8gemm_block128(const void* A, const void* Bt, void* C, int 
     return simt::launch<simt::kFp8Block128>(p, static_cast<cudaStream_t>(stream));
 }
 
-// Variant 3's route knob (reference include/spark/kernels.h:281-294). The reference's tile names are
-// sm_120 tuning artefacts; here the route only says which engine a shape runs on.
+// Variant 3's route knob (reference include/spark/kernels.h:281-294): -1 the per-shape rule, -2 the legacy
+// route (variant 2 where its tile rule holds, else the CUDA cores). The reference's other values force
+// sm_120 tile shapes that do not exist here; they are stored and behave like -1. The name says which
+// kernel of THIS library the shape runs on under the current route, from the launcher's own predicate.
 extern "C" void spk_fp8gemm_v3_set_route(int route) { spk::g_v3_route = route; }
 extern "C" int spk_fp8gemm_v3_route(void) { return spk::g_v3_route; }
-extern "C" int spk_fp8gemm_v3_num_tiles(void) { return 1; }
+extern "C" int spk_fp8gemm_v3_num_tiles(void) { return 2; }  // 128 x 256 and 128 x 128
 extern "C" const char* spk_fp8gemm_v3_route_name(int M, int N, int K, int mx) {
     using namespace spk;
     if (!base_ok(M, N, K) || (mx && K % 256 != 0)) return "unsupported";
-    if (g_v3_route != -2 && tensor_core_shape(M, N, K, sm_count_or(148))) return "umma_128x128";
-    return M <= 64 ? "simt_decode" : "simt";
+    const int v = effective_variant(M, N, K, 3);
+    if (v == 1) return M <= 64 ? "simt_decode" : "simt";
+    const char* plan = fp8gemm_umma_plan(M, N, K, mx != 0, v, true, sm_count_or(148));
+    return plan ? plan : (M <= 64 ? "simt_decode" : "simt");
 }
 extern "C" const char* spk_fp8gemm_v4_route_name(int M, int N, int K) {
     return spk::base_ok(M, N, K) ? "simt_unsplit" : "unsupported";

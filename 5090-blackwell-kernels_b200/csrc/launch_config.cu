@@ -10,6 +10,7 @@
 //   a forced split (decode_force_split_k / SPARK_DECODE_SPLIT) replaces the rule.
 // Named shapes make the rule testable without a GPU: the two the reference names (GB10, RTX 5090)
 // with its constants, and B200 (148 SMs, 126 MB L2, 8 TB/s HBM3e, 1 us loaded latency).
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 
@@ -29,7 +30,7 @@ struct Shape {
 constexpr Shape kGB10 = {48, int64_t{24} << 20, 273.0, 273 * 800, false};
 constexpr Shape kRTX5090 = {170, int64_t{96} << 20, 1792.0, int64_t{64} * 24 * 1024, false};
 constexpr Shape kB200 = {148, int64_t{126} << 20, 8000.0, 8000 * 1000, false};
-constexpr double kL2ResidentShare = 0.75, kWaveFill = 0.875;
+constexpr double kL2ResidentShare = 0.75;
 
 std::atomic<int> g_forced_split{-1};  // -1: SPARK_DECODE_SPLIT not read yet
 
@@ -90,32 +91,36 @@ int need_ctas(int64_t per_cta, const Shape& d) {
     return static_cast<int>(n > 1 ? n : 1);
 }
 
-double last_wave_fill(int64_t ctas, int slots) {
-    if (slots <= 0 || ctas <= 0) return 0.0;
-    return static_cast<double>(ctas) / static_cast<double>(cdiv64(ctas, slots) * slots);
-}
+// ctas CTAs on `slots` resident slots run in ceil(ctas / slots) waves; the last one is what a split can
+// waste. Fractions are compared exactly, as integers: fill = ctas / (waves * slots).
+struct WaveFill {
+    int64_t ctas, capacity;  // capacity = waves * slots
+    bool at_least_seven_eighths() const { return 8 * ctas >= 7 * capacity; }
+    bool fuller_than(const WaveFill& o) const { return ctas * o.capacity > o.ctas * capacity; }
+};
 
+WaveFill wave_fill(int64_t ctas, int slots) { return {ctas, cdiv64(ctas, slots) * slots}; }
+
+// Little's law first: enough CTAs that their copies in flight cover bandwidth x latency, spread over
+// the tiles. When that many CTAs do not fit at once anyway (need > slots) the tail wave is paid
+// whatever the split, so among the splits up to twice the minimum the first whose waves are at least
+// 7/8 full wins, and failing that the fullest. A forced split overrides everything.
 int split_rule(int tiles, int max_split, int64_t per_cta, int slots, const Shape& d) {
-    tiles = tiles > 1 ? tiles : 1;
-    max_split = max_split > 1 ? max_split : 1;
+    tiles = std::max(tiles, 1);
+    max_split = std::max(max_split, 1);
     const int need = need_ctas(per_cta, d);
-    int split = std::min(std::max(cdiv(need, tiles), 1), max_split);
+    int split = std::clamp(cdiv(need, tiles), 1, max_split);
     if (slots > 0 && need > slots) {
-        int best = split;
-        double best_fill = last_wave_fill(static_cast<int64_t>(tiles) * split, slots);
-        const int hi = std::min(max_split, 2 * split);
-        for (int s = split; s <= hi; ++s) {
-            const double f = last_wave_fill(static_cast<int64_t>(tiles) * s, slots);
-            if (f >= kWaveFill) {
-                best = s;
-                break;
-            }
-            if (f > best_fill) best = s, best_fill = f;
+        const int last = std::min(max_split, 2 * split);
+        int chosen = split;
+        WaveFill best = wave_fill(static_cast<int64_t>(tiles) * split, slots);
+        for (int s = split; s <= last && !best.at_least_seven_eighths(); ++s) {
+            const WaveFill f = wave_fill(static_cast<int64_t>(tiles) * s, slots);
+            if (f.at_least_seven_eighths() || f.fuller_than(best)) chosen = s, best = f;
         }
-        split = best;
+        split = chosen;
     }
-    const int forced = forced_split();
-    if (forced > 0) split = std::min(std::max(forced, 1), max_split);
+    if (const int forced = forced_split(); forced > 0) split = std::clamp(forced, 1, max_split);
     return split;
 }
 

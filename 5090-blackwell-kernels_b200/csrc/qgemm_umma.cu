@@ -325,10 +325,10 @@ int launch_umma(const simt::Params& q, const unsigned char* sfa, const unsigned 
         !umma::make_map_2d_u8(&map_b, q.Bt, row_bytes, static_cast<uint64_t>(q.N), BN))
         return fail(SPK_CUDA_ERROR, "umma gemm: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
     auto kernel = qgemm_umma_kernel<BN, MODE>;
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev->device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-        configured[dev->device & 15] = true;
+        configured[dev->device] = true;
     }
     UmmaParams p{};
     p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
@@ -457,6 +457,9 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         int s = 0;
         unsigned ph = 0;
         bool ok = true;
+        // a stage is complete only once the tokens are in, and those are requested after the kernel in front
+        // of a chained launch has completed: the bounded waits below start counting from there
+        pdl_wait();
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
             ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, p.status));
             if (!ok) break;
@@ -576,10 +579,10 @@ int launch_decode(const simt::Params& q, const unsigned char* sfw, const unsigne
         !umma::make_map_2d_u8(&map_x, q.A, row_bytes, static_cast<uint64_t>(q.M), NT))
         return fail(SPK_CUDA_ERROR, "umma decode gemm: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
     auto kernel = qgemm_umma_decode_kernel<NT, MODE>;
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev->device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-        configured[dev->device & 15] = true;
+        configured[dev->device] = true;
     }
     DecodeParams p{};
     p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
@@ -788,10 +791,10 @@ int launch_block128(const simt::Params& q, DeviceState* dev, cudaStream_t stream
         !umma::make_map_2d_u8(&map_b, q.Bt, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), BN))
         return fail(SPK_CUDA_ERROR, "fp8gemm_block128: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
     auto kernel = qgemm_umma_block128_kernel<BN>;
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev->device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-        configured[dev->device & 15] = true;
+        configured[dev->device] = true;
     }
     Block128Params p{};
     p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
@@ -820,7 +823,28 @@ bool umma_disabled() {
     return e && *e == '1';
 }
 
+// 128 x 256 tiles when they fill the SMs once, 128 x 128 tiles otherwise (twice the CTAs on small problems).
+bool wide_tiles(int M, int N, int sms) { return N % 256 == 0 && static_cast<long long>(cdiv(M, kBM)) * (N / 256) >= sms; }
+
 }  // namespace
+
+// Which tensor-core kernel variant 3 (and 2) of fp8gemm runs for a shape, or nullptr when the shape stays on
+// the CUDA cores. One predicate for the launcher and for fp8gemm_v3_route_name.
+const char* fp8gemm_umma_plan(int M, int N, int K, bool mx, int variant, bool c_aligned, int sms) {
+    if (umma_disabled()) return nullptr;
+    const bool decode = M <= 64;
+    if (decode ? variant != 3 : !c_aligned) return nullptr;  // variant 2 keeps the reference's tile rule
+    simt::Params p{};
+    p.M = M, p.N = N, p.K = K;
+    size_t sf_bytes = 0;
+    if (mx) {
+        const int cols = K / 32;
+        sf_bytes = (static_cast<size_t>(cdiv(M, 128)) + cdiv(N, 128)) * 128 * cols;
+        if (sf_bytes > static_cast<size_t>(kPartialFloats) * sizeof(float)) return nullptr;  // scratch too small
+    }
+    if (decode) return decode_fits(p, sf_bytes) ? "umma_decode_splitk" : nullptr;
+    return wide_tiles(M, N, sms) ? "umma_128x256" : "umma_128x128";
+}
 
 // Variant 3 (and 2) of fp8gemm: every shape with M > 64 runs on the tensor cores as 128 x BN tiles, and
 // variant 3 takes M <= 64 with the weights as the 128-row operand and K split over the SMs. In MX mode the
@@ -828,25 +852,18 @@ bool umma_disabled() {
 int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t stream, bool* taken) {
     *taken = false;
     if (umma_disabled()) return SPK_OK;
-    const bool decode = p.M <= 64;
-    if (decode ? variant != 3 : !aligned16(p.C)) return SPK_OK;  // variant 2 keeps the reference's tile rule
     DeviceState* dev = nullptr;
     if (int rc = device_state(&dev)) return rc;
+    if (fp8gemm_umma_plan(p.M, p.N, p.K, mx, variant, aligned16(p.C), dev->sm_count) == nullptr) return SPK_OK;
+    const bool decode = p.M <= 64;
+    const bool wide = wide_tiles(p.M, p.N, dev->sm_count);
+    *taken = true;
     if (!mx) {
-        if (decode) {
-            if (!decode_fits(p, 0)) return SPK_OK;
-            *taken = true;
-            return launch_decode_nt<kFp8>(p, nullptr, nullptr, dev->partials, dev, stream);
-        }
-        *taken = true;
-        return p.N % 256 == 0 ? launch_umma<256, kFp8>(p, nullptr, nullptr, dev, stream)
-                              : launch_umma<128, kFp8>(p, nullptr, nullptr, dev, stream);
+        if (decode) return launch_decode_nt<kFp8>(p, nullptr, nullptr, dev->partials, dev, stream);
+        return wide ? launch_umma<256, kFp8>(p, nullptr, nullptr, dev, stream) : launch_umma<128, kFp8>(p, nullptr, nullptr, dev, stream);
     }
     const int cols = p.K / 32;
     const size_t a_bytes = static_cast<size_t>(cdiv(p.M, 128)) * 128 * cols, b_bytes = static_cast<size_t>(cdiv(p.N, 128)) * 128 * cols;
-    if (a_bytes + b_bytes > static_cast<size_t>(kPartialFloats) * sizeof(float)) return SPK_OK;  // scratch too small
-    if (decode && !decode_fits(p, a_bytes + b_bytes)) return SPK_OK;
-    *taken = true;
     unsigned char* sfa = reinterpret_cast<unsigned char*>(dev->partials);
     unsigned char* sfb = sfa + a_bytes;
     const long long wa = static_cast<long long>(a_bytes / 4), wb = static_cast<long long>(b_bytes / 4);
@@ -857,34 +874,37 @@ int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t s
     if (decode)  // the split-K partials live behind the repacked scales
         rc = launch_decode_nt<kFp8Mx>(p, sfb, sfa, dev->partials + (a_bytes + b_bytes) / 4, dev, stream);
     else
-        rc = p.N % 256 == 0 ? launch_umma<256, kFp8Mx>(p, sfa, sfb, dev, stream) : launch_umma<128, kFp8Mx>(p, sfa, sfb, dev, stream);
+        rc = wide ? launch_umma<256, kFp8Mx>(p, sfa, sfb, dev, stream) : launch_umma<128, kFp8Mx>(p, sfa, sfb, dev, stream);
     if (rc != SPK_OK) return rc;
     // the scratch is shared with the split-K kernels, which expect it zeroed
     SPK_CUDA(cudaMemsetAsync(sfa, 0, a_bytes + b_bytes, stream));
     return SPK_OK;
 }
 
-// Variant 2 of fp4gemm (M and N multiples of 128 by its rule) and the decode route of variant 1 (M <= 64).
+// fp4gemm on the tensor cores: variants 1 and 2 at every M > 64 (TMA zero-fills the rows past M and the
+// blocked scale layout is padded to 128 rows already, so ragged shapes need nothing special), and the
+// split-K decode kernel for M <= 64 (reached through variant 1).
 int fp4gemm_umma_try(const simt::Params& p, int format, cudaStream_t stream, bool* taken) {
     *taken = false;
     if (umma_disabled()) return SPK_OK;
     DeviceState* dev = nullptr;
-    if (p.M <= 64) {  // decode: reached through variant 1
+    if (p.M <= 64) {
         if (!decode_fits(p, 0)) return SPK_OK;
         if (int rc = device_state(&dev)) return rc;
         *taken = true;
         return format == SPK_FP4_NVFP4 ? launch_decode_nt<kNvfp4>(p, p.sfb, p.sfa, dev->partials, dev, stream)
                                        : launch_decode_nt<kMxfp4>(p, p.sfb, p.sfa, dev->partials, dev, stream);
     }
-    if (p.M % 128 != 0 || p.N % 128 != 0 || !aligned16(p.C)) return SPK_OK;
+    if (!aligned16(p.C)) return SPK_OK;
     if (int rc = device_state(&dev)) return rc;
     *taken = true;
+    const bool wide = wide_tiles(p.M, p.N, dev->sm_count);
     if (format == SPK_FP4_NVFP4)
-        return p.N % 256 == 0 ? launch_umma<256, kNvfp4>(p, p.sfa, p.sfb, dev, stream)
-                              : launch_umma<128, kNvfp4>(p, p.sfa, p.sfb, dev, stream);
-    return p.N % 256 == 0 ? launch_umma<256, kMxfp4>(p, p.sfa, p.sfb, dev, stream)
-                          : launch_umma<128, kMxfp4>(p, p.sfa, p.sfb, dev, stream);
+        return wide ? launch_umma<256, kNvfp4>(p, p.sfa, p.sfb, dev, stream) : launch_umma<128, kNvfp4>(p, p.sfa, p.sfb, dev, stream);
+    return wide ? launch_umma<256, kMxfp4>(p, p.sfa, p.sfb, dev, stream) : launch_umma<128, kMxfp4>(p, p.sfa, p.sfb, dev, stream);
 }
+
+namespace {
 
 // ---- fp32-block-scaled fp8 at decode shapes (M <= 64) -----------------------------------------------
 //
@@ -982,6 +1002,7 @@ qgemm_umma_decode_block128_kernel(const __grid_constant__ CUtensorMap map_w, con
         int s = 0;
         unsigned ph = 0;
         bool ok = true;
+        pdl_wait();  // as in the plain decode kernel: count the bounded waits from the predecessor's completion
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
             const int i = kb - kb0, buf = i & 1;
             ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, p.status) && mbar_wait(&tfree[buf], ((i >> 1) & 1) ^ 1, p.status));
@@ -1104,10 +1125,10 @@ int launch_decode_block128(const simt::Params& q, DeviceState* dev, cudaStream_t
         !umma::make_map_2d_u8(&map_x, q.A, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M), NT))
         return fail(SPK_CUDA_ERROR, "fp8gemm_block128: cuTensorMapEncodeTiled failed for %dx%dx%d", q.M, q.N, q.K);
     auto kernel = qgemm_umma_decode_block128_kernel<NT>;
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev->device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-        configured[dev->device & 15] = true;
+        configured[dev->device] = true;
     }
     DecodeBlkParams p{};
     p.C = q.C, p.M = q.M, p.N = q.N, p.K = q.K;
@@ -1118,6 +1139,8 @@ int launch_decode_block128(const simt::Params& q, DeviceState* dev, cudaStream_t
     SPK_CUDA(launch_chained(kernel, dim3(p.n_tiles * p.split), dim3(192), Cfg::kSmem, stream, map_w, map_x, p));
     return SPK_OK;
 }
+
+}  // namespace
 
 // The fp32-block-scaled fp8 GEMM on the tensor cores (every shape; C rows must be 16-byte aligned).
 int fp8gemm_block128_umma_try(const simt::Params& q, cudaStream_t stream, bool* taken) {

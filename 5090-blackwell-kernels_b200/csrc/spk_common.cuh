@@ -60,6 +60,10 @@ struct DeviceState {
     bool ready = false;
 };
 
+// Device ordinals the library keeps state for; device_state() refuses larger ones, so every per-device
+// table below is indexed by an ordinal that has passed that check.
+constexpr int kMaxDevices = 16;
+
 constexpr int64_t kPartialFloats = int64_t{64} * 65536;  // 64 tokens x 65536 columns, 16 MiB
 constexpr int kCounters = 1 << 16;
 constexpr int kStatusWords = 8;

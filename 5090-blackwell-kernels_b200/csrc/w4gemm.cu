@@ -562,10 +562,10 @@ int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target
     StreamParams p = base;
     auto kernel = w4_stream_kernel<MT, NS, CG, ST, ASYM, DUAL>;
     constexpr int smem_max = stream_smem_bytes<ActRing<MT>::kStages, NS, CG, ST, ASYM>(8 * MT);
-    static bool configured[16] = {};
-    if (!configured[dev.device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev.device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
-        configured[dev.device & 15] = true;
+        configured[dev.device] = true;
     }
     p.rows_max = std::min(p.M, 8 * MT);
     const int smem = stream_smem_bytes<ActRing<MT>::kStages, NS, CG, ST, ASYM>(p.rows_max);
@@ -576,8 +576,8 @@ int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target
     if (static_cast<int64_t>(p.M) * p.N > kPartialFloats || static_cast<int64_t>(m_chunks) * p.T > kCounters)
         whole = true;
     p.whole = whole ? 1 : 0;
-    static int occupancy[16][8 * MT + 1] = {};  // per device and activation-ring height
-    int& occ = occupancy[dev.device & 15][p.rows_max];
+    static int occupancy[kMaxDevices][8 * MT + 1] = {};  // per device and activation-ring height
+    int& occ = occupancy[dev.device][p.rows_max];
     if (occ == 0) {
         SPK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kStreamWarps * 32, smem));
         if (occ < 1) return fail(SPK_CUDA_ERROR, "w4gemm: stream kernel does not fit an SM (smem %d)", smem);
@@ -730,6 +730,12 @@ extern "C" int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void*
 // kernel runs (a memset on the same stream), because the array keeps whatever the previous call
 // left; two calls that overlap on the GPU (different streams, no dependency) race on it and must
 // be ordered by the caller.
+//
+// Errors on the device: a bounded wait that gives up inside this entry point's kernel records
+// SPK_TIMEOUT in a status word that also lives in the fixed array. spk_device_status() does not see
+// that word (it reads the arena's, and creating the arena allocates); spk_w4gemm_noalloc_status()
+// reads and clears it without allocating anything. The per-call clearing leaves the status word
+// alone, so a timeout stays visible until it is read.
 namespace spk {
 namespace {
 
@@ -748,7 +754,7 @@ struct NoAllocDevice {
     unsigned char* base = nullptr;  // device address of g_noalloc_scratch on this device
     int sm_count = 0;
 };
-NoAllocDevice g_noalloc[16];
+NoAllocDevice g_noalloc[kMaxDevices];
 
 // Set-up of the current device (first call on it): resolve the array's device address and read the
 // SM count. No allocation; cudaGetSymbolAddress may initialise the context and load the module,
@@ -756,7 +762,7 @@ NoAllocDevice g_noalloc[16];
 int noalloc_device(int* dev_out, NoAllocDevice** out) {
     int dev = 0;
     SPK_CUDA(cudaGetDevice(&dev));
-    SPK_REQUIRE(dev >= 0 && dev < 16, "w4gemm_noalloc: device ordinal %d not supported (max 16)", dev);
+    SPK_REQUIRE(dev >= 0 && dev < kMaxDevices, "w4gemm_noalloc: device ordinal %d not supported (max %d)", dev, kMaxDevices);
     NoAllocDevice& d = g_noalloc[dev];
     if (d.base == nullptr) {
         int major = 0, sms = 0;
@@ -806,7 +812,7 @@ extern "C" int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, con
 
     // The array keeps the last call's contents: clear what this call will accumulate into.
     SPK_CUDA(cudaMemsetAsync(state.partials, 0, static_cast<size_t>(M) * N * sizeof(float), stream));
-    SPK_CUDA(cudaMemsetAsync(state.counters, 0, kNoAllocCounterBytes + kNoAllocStatusBytes, stream));
+    SPK_CUDA(cudaMemsetAsync(state.counters, 0, kNoAllocCounterBytes, stream));  // not the status word behind them
 
     StreamParams p{};
     p.A = static_cast<const __nv_bfloat16*>(A);
@@ -823,4 +829,24 @@ extern "C" int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, con
     p.counters = state.counters;
     p.status = state.status;
     return zeros ? launch_stream<true>(p, false, state, stream) : launch_stream<false>(p, false, state, stream);
+}
+
+// Reads the status word of the fixed array on the current device (SPK_OK, or SPK_TIMEOUT after a
+// bounded wait of spk_w4gemm_bf16_noalloc's kernel gave up), waits for `stream`, and clears the word
+// if it was set. Like the GEMM entry point it allocates nothing: the word is copied straight from
+// the array's device address. A result produced by a call that timed out is incomplete; run it again.
+extern "C" int spk_w4gemm_noalloc_status(void* stream_, int* code) {
+    using namespace spk;
+    SPK_REQUIRE(code != nullptr, "w4gemm_noalloc_status: null code");
+    int dev = 0;
+    NoAllocDevice* nd = nullptr;
+    if (int rc = noalloc_device(&dev, &nd)) return rc;
+    auto stream = static_cast<cudaStream_t>(stream_);
+    int* word = reinterpret_cast<int*>(nd->base + kNoAllocPartialBytes + kNoAllocCounterBytes);
+    int host = 0;
+    SPK_CUDA(cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    SPK_CUDA(cudaStreamSynchronize(stream));
+    if (host != 0) SPK_CUDA(cudaMemsetAsync(word, 0, sizeof(int), stream));
+    *code = host;
+    return SPK_OK;
 }

@@ -129,7 +129,8 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     uint64_t* acc_ready = a_free + kChunkStages;  // [2] MMA commit
     uint64_t* acc_free = acc_ready + 2;           // [2] 4 epilogue warps
     uint64_t* code_bar = acc_free + 2;            // [DW][kCodeSlots]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(code_bar + DW * kCodeSlots);
+    uint64_t* drain_bar = code_bar + DW * kCodeSlots;  // MMA commit on the error path only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
 
     pdl_release();  // a chained kernel behind this one may become resident as this grid's CTAs exit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,6 +159,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             mbar_init(&acc_ready[lane], 1);
             mbar_init(&acc_free[lane], 4);
         }
+        if (lane == 2) mbar_init(drain_bar, 1);
         ptx::fence_mbar_init();
         if (lane == 0) umma::prefetch_tensormap(&map_act);
     }
@@ -176,8 +178,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         uint64_t* my_bar = code_bar + warp * kCodeSlots;
         // next chunk to fetch: this warp takes chunks f0 + set, f0 + set + 2, ...
         int pf = f0 + set, p_slot = 0, p_ss = pf / chunks, p_ch = pf - p_ss * chunks;
+        int n_issued = 0;
         auto issue = [&]() {
             if (pf >= f1) return;
+            ++n_issued;
             const int t = p_ss * kStrips + strip, g0 = p_ch * kChunkGroups;
             unsigned char* slot = ring + p_slot * L::kSlotBytes;
             uint64_t* bar = &my_bar[p_slot];
@@ -204,8 +208,9 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         const int n_mine = n_chunks > set ? (n_chunks - set + 1) / 2 : 0;
         int slot_i = 0, cs = set;  // chunk stage of local chunk index set, set + 2, ...
         unsigned code_ph = 0, ph = 0;
-        bool ok = true;
-        for (int it = 0; it < n_mine && ok; ++it) {
+        bool ok = true, chained = false;
+        int it = 0;
+        for (; it < n_mine && ok; ++it) {
             ok = __all_sync(0xffffffffu, mbar_wait(&my_bar[slot_i], code_ph, p.status));
             if (!ok) break;
             const unsigned char* slot = ring + slot_i * L::kSlotBytes;
@@ -230,6 +235,14 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                     w4::dequant_word(q.w, o_lo, o_hi, s_lo, s_hi, x[h][3]);
                 }
                 if (sub == 0) {  // the stage is free once the MMAs of three chunks ago have read it
+                    // The first kChunkStages chunks find their stage fresh. From then on the wait depends on
+                    // the MMA warp, which needs activations that exist only once the kernel in front of a
+                    // chained launch has completed: wait for that first, so that the poll budget below
+                    // measures this kernel's pipeline and not how long the predecessor still runs.
+                    if (!chained && set + kSets * it >= kChunkStages) {
+                        pdl_wait();
+                        chained = true;
+                    }
                     ok = __all_sync(0xffffffffu, mbar_wait(&a_free[cs], ph ^ 1u, p.status));
                     if (!ok) break;
                     umma::fence_after_sync();
@@ -257,6 +270,15 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(&a_ready[cs]);
             cs += kSets;
             if (cs >= kChunkStages) cs -= kChunkStages, ph ^= 1u;
+        }
+        if (!ok) {
+            // A wait gave up: let the code copies still in flight into this warp's ring land (bounded,
+            // no status) before the CTA may exit and its shared memory be handed to another CTA.
+            const int outstanding = n_issued - it;
+            for (int j = 1; j < outstanding && j < kCodeSlots; ++j) {
+                const int sj = slot_i + j < kCodeSlots ? slot_i + j : slot_i + j - kCodeSlots;
+                (void)mbar_wait(&my_bar[sj], sj > slot_i ? code_ph : code_ph ^ 1u, nullptr);
+            }
         }
     } else if (warp == kProducerWarp0) {
         // ================= activation producer: one 128-k group (two units) per slot =================
@@ -286,6 +308,9 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         int seg = 0, cs = 0, as = 0, ch = f0 % chunks;
         unsigned ph = 0, aph = 0;
         bool ok = true, fresh = true;
+        // Everything this warp waits for needs the activations, which the producer requests only after the
+        // kernel in front of a chained launch has completed; its bounded waits start counting from there.
+        pdl_wait();
         for (int f = f0; f < f1 && ok; ++f) {
             const int buf = seg & 1;
             if (fresh) {
@@ -324,6 +349,13 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             if (++cs == kChunkStages) cs = 0, ph ^= 1u;
             if (seg_end) ++seg, fresh = true;
             if (++ch == chunks) ch = 0;
+        }
+        if (!ok) {
+            // MMAs already issued may still be reading TMEM and shared memory: one more commit, and a
+            // bounded wait for it, before the CTA frees them.
+            if (umma::elect_one()) umma::mma_commit(drain_bar);
+            __syncwarp();
+            (void)mbar_wait(drain_bar, 0, nullptr);
         }
     } else {
         // ================= epilogue warps: TMEM lane quarter = warp % 4 =================
@@ -441,10 +473,10 @@ int launch_w4_tmem(const void* A, W4TmemParams p, DeviceState* dev, cudaStream_t
     if (!umma::make_map_2d_u8(&map_act, dev->act_scratch, static_cast<uint64_t>(p.K) * 2, static_cast<uint64_t>(p.M), NT))
         return fail(SPK_CUDA_ERROR, "w4gemm: cuTensorMapEncodeTiled failed for M=%d K=%d", p.M, p.K);
     auto kernel = w4_tmem_kernel<NT, ASYM>;
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev->device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-        configured[dev->device & 15] = true;
+        configured[dev->device] = true;
     }
     p.super_strips = p.N / 128;
     const long long total = static_cast<long long>(p.super_strips) * (p.G / kChunkGroups);

@@ -374,10 +374,10 @@ int launch_w4_umma(const void* A, W4UmmaParams p, DeviceState* dev, cudaStream_t
     if (!umma::make_map_2d_u8(&map_act, A, static_cast<uint64_t>(p.K) * 2, static_cast<uint64_t>(p.M), NT))
         return fail(SPK_CUDA_ERROR, "w4gemm: cuTensorMapEncodeTiled failed for M=%d K=%d", p.M, p.K);
     auto kernel = w4_umma_kernel<NT, ASYM>;
-    static bool configured[16] = {};
-    if (!configured[dev->device & 15]) {
+    static bool configured[kMaxDevices] = {};
+    if (!configured[dev->device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-        configured[dev->device & 15] = true;
+        configured[dev->device] = true;
     }
     p.super_strips = p.N / 128;
     const long long total = static_cast<long long>(p.super_strips) * (p.G / kChunkGroups);

@@ -48,6 +48,8 @@ _spk_w4_quantize = _sig("spk_w4_quantize_bf16", [_p, _p, _p, _p, _i, _i, _p])
 _spk_w4_repack = _sig("spk_w4_repack", [_p, _p, _i, _i, _p])
 _spk_w4gemm = _sig("spk_w4gemm_bf16", [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
 _spk_w4gemm_noalloc = _sig("spk_w4gemm_bf16_noalloc", [_p, _p, _p, _p, _p, _i, _i, _i, _p])
+_spk_w4gemm_noalloc_status = _sig("spk_w4gemm_noalloc_status", [_p, ctypes.POINTER(_i)])
+_spk_debug_expire_wait = _sig("spk_debug_expire_wait", [_i, _p])
 _sig("spk_w4gemm_num_variants", [])
 _sig("spk_w4gemm_default_variant", [])
 _sig("spk_w4gemm_supports", [_i, _i, _i, _i])
@@ -223,6 +225,37 @@ def w4gemm_noalloc(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
         _status(_spk_w4gemm_noalloc(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros),
                                     out.data_ptr(), M, N, K, _stream(a)))
     return out
+
+
+def w4gemm_noalloc_status(device=None) -> int:
+    """Waits for the current stream and returns the status word of `w4gemm_noalloc` on the device
+    (0, or 3 after a bounded wait of its kernel gave up), clearing it. Allocates nothing; it is not
+    the word `device_status` reads."""
+    code = _i(0)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _status(_spk_w4gemm_noalloc_status(torch.cuda.current_stream(dev).cuda_stream, ctypes.byref(code)))
+    return code.value
+
+
+def debug_expire_wait(dirty: int = 0, device=None) -> None:
+    """Test hook: a kernel whose bounded wait runs out (status 3 afterwards) and that leaves `dirty`
+    words of the split-K scratch non-zero, as an interrupted GEMM would."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _status(_spk_debug_expire_wait(int(dirty), torch.cuda.current_stream(dev).cuda_stream))
+
+
+_spk_stream_probe = _sig("spk_stream_probe", [_p, ctypes.c_longlong, _i, _i, _p])
+
+
+def stream_probe(buf: torch.Tensor, ctas: int, depth: int) -> None:
+    """Read-only stream over `buf` (CUDA, contiguous, a multiple of 4096 bytes) by `ctas` CTAs with
+    `depth` 4 KiB bulk copies in flight each; time it with CUDA events (launch-rule calibration, read floor)."""
+    _check_cuda_contig(buf, "buf")
+    nbytes = buf.numel() * buf.element_size()
+    with torch.cuda.device(buf.device):
+        _status(_spk_stream_probe(buf.data_ptr(), nbytes, int(ctas), int(depth), _stream(buf)))
 
 
 # ---- fp8 --------------------------------------------------------------------------------------

@@ -41,8 +41,16 @@ SPK_API const char* spk_version(void);
  * capturing a CUDA graph so that no allocation happens during capture. */
 SPK_API int spk_init(void);
 /* Synchronizes the stream and reads the device status word: *code is SPK_OK unless a kernel's
- * bounded wait timed out (SPK_TIMEOUT); the word is cleared. */
+ * bounded wait timed out (SPK_TIMEOUT). After a timeout the word is cleared and the shared split-K
+ * scratch (which the interrupted kernel may have left half summed) is zeroed again on `stream`;
+ * the outputs of the GEMMs launched since the last clean status are not to be trusted: run them
+ * again. Does not cover spk_w4gemm_bf16_noalloc, which has its own status call below. */
 SPK_API int spk_device_status(void* stream, int* code);
+/* Test hook, no counterpart in the reference: launches a one-block kernel that leaves `dirty` words of
+ * the split-K scratch non-zero, waits a few thousand polls for a barrier phase nothing completes and
+ * records SPK_TIMEOUT, i.e. the state a broken pipeline would leave. No fault, no trap; the context
+ * stays usable. */
+SPK_API int spk_debug_expire_wait(int dirty, void* stream);
 
 /* ---- int4 W4A16 ------------------------------------------------------------------------- */
 
@@ -71,6 +79,12 @@ SPK_API int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void* sc
  * on the GPU race on it, so order them. */
 SPK_API int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, const void* scales,
                                     const uint8_t* zeros, void* C, int M, int N, int K, void* stream);
+/* No counterpart in the reference. The status word of spk_w4gemm_bf16_noalloc lives in the same fixed
+ * array and is NOT the one spk_device_status reads (that call creates the per-device arena, i.e. it
+ * allocates). This call waits for `stream`, returns the word in *code (SPK_OK or SPK_TIMEOUT) and
+ * clears it, without allocating. A GEMM call does not clear the word, so a timeout stays visible
+ * until it is read here. */
+SPK_API int spk_w4gemm_noalloc_status(void* stream, int* code);
 /* reference include/spark/kernels.h:414-416 */
 SPK_API int spk_w4gemm_num_variants(void);
 SPK_API int spk_w4gemm_default_variant(void);
@@ -158,6 +172,12 @@ SPK_API int spk_decode_need_ctas(int64_t per_cta_in_flight, int device);
 SPK_API int spk_decode_fits_l2(int64_t bytes, int device);
 SPK_API void spk_decode_force_split_k(int split);
 SPK_API int spk_decode_forced_split_k(void);
+/* No counterpart in the reference's API (its docs describe the measurement, docs/design/hgemm.md:235-244):
+ * a read-only stream of `bytes` (a multiple of 4096) from `src` by `ctas` CTAs, each keeping `depth`
+ * 4 KiB bulk copies in flight (1..48). Time it with events: the CTA-count sweep gives the loaded
+ * latency and the bytes in flight behind the B200 constants of the launch rule, and it is the floor
+ * the decode GEMMs are compared with. */
+SPK_API int spk_stream_probe(const void* src, long long bytes, int ctas, int depth, void* stream);
 
 /* ---- push all-reduce for the row-split projections of a tensor-parallel layer ---------------
  * No counterpart in the reference (it is single GPU). One process per GPU of one node: every rank

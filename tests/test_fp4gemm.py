@@ -12,7 +12,9 @@ pytestmark = pytest.mark.gpu
 # the last two have at least one 128 x 128 tile per SM, which variant 2 (tensor cores) asks for:
 # one with N % 256 == 0 (128 x 256 tiles) and one without (128 x 128 tiles)
 SHAPES = [(16, 64, 256), (1, 128, 256), (5, 64, 512), (64, 256, 1024), (100, 128, 256), (16, 4096, 4096),
-          (128, 256, 512), (256, 512, 1024), (2048, 2560, 512), (1536, 1664, 256)]
+          (128, 256, 512), (256, 512, 1024), (2048, 2560, 512), (1536, 1664, 256),
+          # ragged and few-tile shapes above 64 tokens: the default route must stay on the tensor cores
+          (100, 4096, 256), (300, 4096, 512), (640, 4096, 256)]
 
 
 @pytest.mark.parametrize("rows,K", [(1, 256), (100, 1024), (128, 4096), (300, 14336)])

@@ -145,11 +145,19 @@ def test_fp8gemm_same_bits_every_run(sk, orc):
 
 def test_fp8gemm_batch_invariant_rows(sk, orc):
     """Variant 4: row i has the same bits whatever M is."""
-    qa, sa, qb, sb = _inputs(orc, 130, 256, 512, 5)
+    qa, sa, qb, sb = _inputs(orc, 513, 256, 512, 5)
     B, SA, SB = _e4m3(qb), torch.from_numpy(sa).cuda(), torch.from_numpy(sb).cuda()
     full = sk.fp8gemm(_e4m3(qa), B, SA, SB, variant=4)
-    for M in (1, 3, 16, 17, 64, 65, 129):
+    ms = (1, 3, 16, 17, 64, 65, 129, 257, 512)  # the reference's list goes to 513 (tests/test_batch_invariant.py:99-152)
+    for M in ms:
         assert torch.equal(sk.fp8gemm(_e4m3(qa[:M]), B, SA, SB, variant=4), full[:M]), M
+    # and with MX block scales
+    qa, sfa, qb, sfb = _mx_inputs(orc, 513, 256, 512, 6)
+    B, SFB = _e4m3(qb), torch.from_numpy(sfb).cuda()
+    full = sk.fp8gemm(_e4m3(qa), B, sfa=torch.from_numpy(sfa).cuda(), sfb=SFB, variant=4)
+    for M in ms:
+        got = sk.fp8gemm(_e4m3(qa[:M]), B, sfa=torch.from_numpy(np.ascontiguousarray(sfa[:M])).cuda(), sfb=SFB, variant=4)
+        assert torch.equal(got, full[:M]), ("mx", M)
 
 
 def test_fp8gemm_block128_matches_oracle(sk, orc):
@@ -189,7 +197,27 @@ def test_fp8gemm_rejects_bad_input(sk):
     with pytest.raises(RuntimeError):
         sk.fp8gemm(a, b, one, one, variant=5)
     assert sk.num_variants("fp8gemm") == 5
-    prev = sk._C.fp8gemm_v3_set_route(-2)
-    assert sk._C.fp8gemm_v3_route_name(4096, 4096, 4096).startswith("simt")
-    sk._C.fp8gemm_v3_set_route(prev)
     assert isinstance(sk._C.fp8gemm_v4_route_name(64, 4096, 4096), str)
+
+
+def test_fp8gemm_v3_route_changes_what_runs(sk, orc):
+    """The route knob of variant 3 (reference include/spark/kernels.h:281-294): -1 is the per-shape rule,
+    -2 the legacy route (variant 2 where its tile rule holds, else the CUDA cores). The name reports the
+    kernel the launcher's own predicate picks, and the legacy route really runs the other kernel: its
+    bits equal variant 1's."""
+    name = sk._C.fp8gemm_v3_route_name
+    assert name(4096, 4096, 4096) == "umma_128x256" and name(16, 4096, 4096) == "umma_decode_splitk"
+    assert name(100, 128, 256) == "umma_128x128" and name(100, 100, 256) == "unsupported"
+    qa, sa, qb, sb = _inputs(orc, 100, 128, 256, 8)
+    args = (_e4m3(qa), _e4m3(qb), torch.from_numpy(sa).cuda(), torch.from_numpy(sb).cuda())
+    v1 = sk.fp8gemm(*args, variant=1)
+    prev = sk._C.fp8gemm_v3_set_route(-2)
+    try:
+        assert sk._C.fp8gemm_v3_route() == -2
+        assert name(100, 128, 256) == "simt" and name(16, 4096, 4096) == "simt_decode"
+        assert name(4096, 4096, 4096) == "umma_128x256"  # variant 2's tile rule holds there
+        legacy = sk.fp8gemm(*args, variant=3)
+    finally:
+        sk._C.fp8gemm_v3_set_route(prev)
+    assert torch.equal(legacy, v1)
+    assert_bf16_close(sk.fp8gemm(*args, variant=3), orc.fp8gemm(qa, qb, sa[0], sb[0]), "default route")

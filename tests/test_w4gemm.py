@@ -124,9 +124,9 @@ def test_w4gemm_batch_invariant_rows(sk):
     """Variant 3: row i of C has the same bits whatever M is and wherever it sits in the batch."""
     K, N = 1152, 256
     ww = sk.W4Weight.quantize(seeded_weight(K, N).cuda())
-    a = seeded_acts(130, K).cuda()
+    a = seeded_acts(513, K).cuda()
     full = sk.w4gemm(a, ww, variant=3)
-    for M in (1, 3, 8, 9, 16, 17, 33, 64, 65, 129):
+    for M in (1, 3, 8, 9, 16, 17, 33, 64, 65, 129, 257, 512):  # the reference's list goes to 513
         assert torch.equal(sk.w4gemm(a[:M].contiguous(), ww, variant=3), full[:M]), M
     assert torch.equal(sk.w4gemm(a[5:6].contiguous(), ww, variant=3), full[5:6])
 
@@ -206,4 +206,25 @@ def test_w4gemm_back_to_back_calls_chain_correctly(sk, orc, M):
             a32, b32 = a.float(), b.float()
             assert torch.isfinite(a32).all(), (attempt, i)
             assert (a32 - b32).abs().max().item() <= 0.03 * b32.abs().max().item(), (attempt, i, M)
+    assert sk._C.device_status() == 0
+
+
+def test_an_expired_wait_is_reported_and_the_scratch_is_clean_again(sk, orc):
+    """A kernel whose bounded wait runs out sets the status word and may leave partial sums and strip
+    counters behind. Reading the status reports it once, restores the scratch, and the next split-K
+    GEMM matches the oracle. (The wait runs out in a test kernel that waits for a barrier phase nothing
+    completes; nothing faults and the context stays usable.)"""
+    K, N = 4096, 4096
+    ww = sk.W4Weight.quantize(seeded_weight(K, N, seed=11).cuda())
+    a = seeded_acts(1, K, seed=12).cuda()
+    want = orc.w4gemm(t2n(a), t2n(ww.packed), t2n(ww.scales), None)
+    assert sk._C.device_status() == 0
+    sk._C.debug_expire_wait(4096)
+    assert sk._C.device_status() == 3
+    assert sk._C.device_status() == 0
+    for M in (1, 64):  # the stream kernel's and the tensor-core kernel's split-K
+        aa = seeded_acts(M, K, seed=12).cuda()
+        assert_bf16_close(sk.w4gemm(aa, ww, variant=2), orc.w4gemm(t2n(aa), t2n(ww.packed), t2n(ww.scales), None),
+                          f"after an expired wait, M={M}")
+    assert_bf16_close(sk.w4gemm(a, ww, variant=2), want, "after an expired wait")
     assert sk._C.device_status() == 0
