@@ -60,6 +60,22 @@ constexpr int kThreadsT = (DW + 6) * 32;
 constexpr int kTmemColsT = 512;
 constexpr int kWeightCol0 = 128;  // first TMEM column of the weight stages
 
+// Development aid, compiled in only with -DSPK_W4_TRACE: device clock stamps of the roles of a few CTAs,
+// written to a buffer set with spk_debug_w4_trace (layout [cta slot][warp][kTraceEvents]).
+#ifdef SPK_W4_TRACE
+constexpr int kTraceEvents = 256, kTraceCtas = 4;
+__device__ unsigned long long* g_w4_trace = nullptr;
+__device__ __forceinline__ void trace_stamp(int warp, int lane, int& n) {
+    const int slot = blockIdx.x == 0 ? 0 : blockIdx.x == 1 ? 1 : blockIdx.x == gridDim.x / 2 ? 2 : blockIdx.x == gridDim.x - 1 ? 3 : -1;
+    if (lane == 0 && slot >= 0 && g_w4_trace != nullptr && n < kTraceEvents)
+        g_w4_trace[(static_cast<size_t>(slot) * 32 + warp) * kTraceEvents + n] = clock64();
+    ++n;
+}
+#define W4_TRACE() trace_stamp(warp, lane, trace_n)
+#else
+#define W4_TRACE() ((void)0)
+#endif
+
 struct W4TmemParams {
     const unsigned char* packed;
     const unsigned char* scales;
@@ -134,6 +150,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
 
     pdl_release();  // a chained kernel behind this one may become resident as this grid's CTAs exit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SPK_W4_TRACE
+    int trace_n = 0;
+#endif
+    W4_TRACE();  // 0: kernel entry
     const int chunks = p.G / kChunkGroups;  // chunks per super-strip
     const long long total = static_cast<long long>(p.super_strips) * chunks;
     const int f0 = static_cast<int>(blockIdx.x * total / gridDim.x);
@@ -168,6 +188,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    W4_TRACE();  // 1: set-up done
 
     if (warp < DW) {
         // ================= dequant warps =================
@@ -211,8 +232,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         bool ok = true, chained = false;
         int it = 0;
         for (; it < n_mine && ok; ++it) {
+            W4_TRACE();  // dequant 2 + 5 it: iteration start
             ok = __all_sync(0xffffffffu, mbar_wait(&my_bar[slot_i], code_ph, p.status));
             if (!ok) break;
+            W4_TRACE();  // + 1: codes landed
             const unsigned char* slot = ring + slot_i * L::kSlotBytes;
             const uint4* cw = reinterpret_cast<const uint4*>(slot);
 #pragma unroll
@@ -243,9 +266,11 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                         pdl_wait();
                         chained = true;
                     }
+                    W4_TRACE();  // + 2: first group dequantized
                     ok = __all_sync(0xffffffffu, mbar_wait(&a_free[cs], ph ^ 1u, p.status));
                     if (!ok) break;
                     umma::fence_after_sync();
+                    W4_TRACE();  // + 3: TMEM stage free
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -264,6 +289,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             __syncwarp();
             issue();
             if (++slot_i == kCodeSlots) slot_i = 0, code_ph ^= 1u;
+            W4_TRACE();  // + 4: stores issued, next copy requested
             tmem_st_wait();
             umma::fence_before_sync();
             __syncwarp();
@@ -318,8 +344,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 if (!ok) break;
             }
             const uint32_t acc = tmem_base + buf * NT;
+            W4_TRACE();  // MMA 2 + 2 chunk: waiting for the chunk's weights
             ok = __all_sync(0xffffffffu, mbar_wait(&a_ready[cs], ph, p.status));
             if (!ok) break;
+            W4_TRACE();  // + 1: weights ready
             for (int sub = 0; sub < kChunkGroups && ok; ++sub) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&act_full[as], aph, p.status));
                 if (!ok) break;
@@ -368,8 +396,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             const int ss = f / chunks, ch = f - ss * chunks;
             if (!(ch == chunks - 1 || f == f1 - 1)) continue;
             const int buf = seg & 1;
+            W4_TRACE();  // epilogue 2 + 3 seg: waiting for a segment
             ok = __all_sync(0xffffffffu, mbar_wait(&acc_ready[buf], (seg >> 1) & 1, p.status));
             if (!ok) break;
+            W4_TRACE();  // + 1: accumulator ready
             umma::fence_after_sync();
             uint32_t v[NT];
 #pragma unroll
@@ -407,7 +437,9 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             }
             ++seg;
             seg_ch0 = 0;
+            W4_TRACE();  // + 2: stored or reduced
         }
+        W4_TRACE();  // before completion
         // completion of the partial segments: one fence, then the per-(tile, quarter) counters
         if (n_pend > 0) {
             __threadfence();
@@ -440,8 +472,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             }
         }
     }
+    W4_TRACE();  // role finished
     umma::fence_before_sync();
     __syncthreads();
+    W4_TRACE();  // CTA finished
     if (warp == kMmaWarp) umma::tmem_dealloc(tmem_base, kTmemColsT);
 }
 
@@ -537,5 +571,11 @@ int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, co
     }
     return SPK_OK;
 }
+
+#ifdef SPK_W4_TRACE
+extern "C" __attribute__((visibility("default"))) int spk_debug_w4_trace(unsigned long long* buf) {
+    return cudaMemcpyToSymbol(g_w4_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 }  // namespace spk

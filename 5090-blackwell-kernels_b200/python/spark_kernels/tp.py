@@ -1,5 +1,5 @@
 """Tensor-parallel sharding of the int4 projections of a Llama-style decoder layer, and the
-full-depth projection stack that runs them (BASELINE config 4). The reference is single GPU; this
+full-depth projection stack that runs them (32 layers at 64 tokens). The reference is single GPU; this
 is the one place the path shards: qkv and gate|up are split by columns (no communication), o and
 down by rows (K), followed by one all-reduce of the [M, hidden] output.
 

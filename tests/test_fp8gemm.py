@@ -213,7 +213,7 @@ def test_fp8gemm_v3_route_changes_what_runs(sk, orc):
     v1 = sk.fp8gemm(*args, variant=1)
     prev = sk._C.fp8gemm_v3_set_route(-2)
     try:
-        assert sk._C.fp8gemm_v3_route() == -2
+        assert sk._C._lib.spk_fp8gemm_v3_route() == -2
         assert name(100, 128, 256) == "simt" and name(16, 4096, 4096) == "simt_decode"
         assert name(4096, 4096, 4096) == "umma_128x256"  # variant 2's tile rule holds there
         legacy = sk.fp8gemm(*args, variant=3)
