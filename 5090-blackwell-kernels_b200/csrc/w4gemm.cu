@@ -144,18 +144,25 @@ w4_strip_kernel(const __nv_bfloat16* __restrict__ A, const uint4* __restrict__ p
 
 // ---- variants 2 and 3: the weight stream ------------------------------------------------------------
 //
+// Arithmetic. Every weight is dequantized exactly as the reference defines it, w = bf16((q - z) * s):
+// an exact bf16 subtraction and one rounding multiplication per pair (15 instructions per 8 weights).
+// Applying the scale once per 128-k group to the fp32 group sum would save the multiplications, and it
+// was built and measured here: it is a DIFFERENT function. The reference's result contains the bf16
+// rounding of every single weight; without it outputs move by ~1e-3 of the output range (sqrt(K) terms
+// of relative error 2^-9 each), which fails the parity tolerance on every output that is small against
+// the range. It also did not run faster: the kernel is not bound by its instruction count.
+//
 // Work decomposition. A super-strip is kStreamWarps * NS strips (128 * NS columns); a chunk is CG
 // groups of one super-strip. Chunks are numbered super-strip major and every CTA takes an equal
-// contiguous range of them, so every SM streams and dequantizes the same amount whatever the
-// shape (the kernel is bound by the ALU pipes as much as by HBM, so balance matters). Warp w
-// owns strips (super * 8 + w) * NS .. + NS - 1 of each super-strip the range touches.
+// contiguous range of them, so every SM streams the same amount whatever the shape. Warp w owns
+// strips (super * 8 + w) * NS .. + NS - 1 of each super-strip the range touches.
 // A K segment that covers a whole strip goes straight to C. A partial one is added to an fp32
 // scratch with fire-and-forget reductions; at the very end of the warp one fence publishes them,
 // a per-strip counter is advanced, and whoever completes a strip converts it to bf16 and leaves
 // scratch and counter zeroed. Variant 3 cuts the ranges at super-strip boundaries instead: no
 // scratch, a fixed summation order.
 //
-// Data movement per warp, private to the warp (no block-level barrier anywhere in the loop):
+// Data movement per consumer warp, private to the warp (no block-level barrier anywhere in the loop):
 //   codes   one bulk asynchronous copy (TMA engine, untiled) per strip per chunk: CG KiB,
 //           contiguous in the repacked layout (2 KiB or more per request: smaller requests
 //           measured well below the HBM rate)
@@ -163,7 +170,42 @@ w4_strip_kernel(const __nv_bfloat16* __restrict__ A, const uint4* __restrict__ p
 // all landing in ring slot (chunk % ST) and all signalled on that slot's mbarrier: the bulk copy
 // through its transaction count, the cp.async copies through one deferred arrive per lane.
 
-constexpr int kStreamWarps = 8;  // warps per CTA, one strip set each, along N
+// Development aid, compiled in only with -DSPK_W4_TRACE: device clock stamps of a few CTAs' warps,
+// written to a buffer set with spk_debug_w4s_trace (layout [cta slot][warp][kTraceEvents]).
+#ifdef SPK_W4_TRACE
+constexpr int kTraceEvents = 256;
+__device__ unsigned long long* g_w4s_trace = nullptr;
+__device__ __forceinline__ void trace_stamp(int warp, int lane, int& n) {
+    const int slot = blockIdx.x == 0 ? 0 : blockIdx.x == 1 ? 1 : blockIdx.x == gridDim.x / 2 ? 2 : blockIdx.x == gridDim.x - 1 ? 3 : -1;
+    if (lane == 0 && slot >= 0 && blockIdx.y == 0 && g_w4s_trace != nullptr && n < kTraceEvents)
+        g_w4s_trace[(static_cast<size_t>(slot) * 32 + warp) * kTraceEvents + n] = clock64();
+    ++n;
+}
+#define W4S_TRACE() trace_stamp(warp, lane, trace_n)
+// grid-level schedule: chip-wide nanosecond timer at entry / after the dependency wait / at the end of
+// warp 0 of EVERY CTA, for successive launches: g_w4s_grid[(launch * 1024 + cta) * 4 + event]
+__device__ unsigned long long* g_w4s_grid = nullptr;
+__device__ unsigned g_w4s_seq[1024];
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define W4S_GRID(ev)                                                                                              \
+    do {                                                                                                          \
+        if (threadIdx.x == 0 && blockIdx.y == 0 && g_w4s_grid != nullptr && blockIdx.x < 1024 && grid_seq < 64)   \
+            g_w4s_grid[(static_cast<size_t>(grid_seq) * 1024 + blockIdx.x) * 4 + (ev)] = globaltimer();         \
+    } while (0)
+#else
+#define W4S_TRACE() ((void)0)
+#define W4S_GRID(ev) ((void)0)
+#endif
+
+#ifndef SPK_STREAM_WARPS
+#define SPK_STREAM_WARPS 8
+#endif
+constexpr int kStreamWarps = SPK_STREAM_WARPS;          // consumer warps per CTA, one strip set each, along N
+constexpr int kStreamThreads = (kStreamWarps + 1) * 32;  // + the activation warp
 
 struct StreamParams {
     const __nv_bfloat16* A;
@@ -189,23 +231,25 @@ struct Slot {
 };
 
 // Activation ring (shared by the CTA): stage j holds, for every token row of this CTA's chunk of
-// tokens, the CG * 128 activations of chunk j. One extra warp streams it with one bulk copy per
-// row; the eight consumer warps read their MMA B operands from it with LDS.128. Activations must
-// live in shared memory: the codes stream through L2 at the HBM rate, and activation loads that
-// miss the small L1 left beside ~200 KiB of shared memory then queue behind that stream
-// (measured: 25% L1 misses doubled the kernel time).
+// tokens, the CG * 128 activations of chunk j.
+// The activation warp streams the rows in with one bulk copy per row; the consumer warps read their
+// MMA B operands from the ring with LDS.128. Activations must live in shared memory: the codes
+// stream through L2 at the HBM rate, and activation loads that miss the small L1 left beside
+// ~200 KiB of shared memory then queue behind that stream (measured: 25% L1 misses doubled the
+// kernel time).
 template <int MT>
 struct ActRing {
-    static constexpr int kStages = MT == 1 ? 8 : (MT == 2 ? 4 : (MT == 4 ? 3 : 2));  // 8 MT rows x (CG x 256 + 64) bytes per stage
+    static constexpr int kStages = MT <= 2 ? 4 : (MT == 4 ? 3 : 2);
 };
 // Row pitch: chunk bytes + 64, so that the eight lanes of a quarter warp (two token rows x four
 // 16-byte columns) fall into distinct 16-byte bank groups.
 __host__ __device__ constexpr int act_pitch(int cg) { return cg * 256 + 64; }
+__host__ __device__ constexpr int act_stage_bytes(int rows, int cg) { return rows * act_pitch(cg); }
 
-template <int AST, int NS, int CG, int ST, bool ASYM>
+template <int MT, int NS, int CG, int ST, bool ASYM>
 constexpr int stream_smem_bytes(int rows) {
-    return kStreamWarps * ST * Slot<NS, CG, ASYM>::kBytes + AST * rows * (CG * 256 + 64) +
-           (2 * AST + kStreamWarps * ST) * 8;
+    return kStreamWarps * ST * Slot<NS, CG, ASYM>::kBytes + ActRing<MT>::kStages * act_stage_bytes(rows, CG) +
+           (2 * ActRing<MT>::kStages + kStreamWarps * ST) * 8;
 }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -217,25 +261,36 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(ptx::smem_u32(bar)) : "memory");
 }
 
-// Resident CTAs the register budget is held to: the loop is bound by instruction issue and two
-// half-rate pipes, and needs six to eight warps per scheduler to keep them busy.
-#ifndef SPK_W4_MINCTAS
-#define SPK_W4_MINCTAS 1
-#endif
+// Resident CTAs the register budget is held to: two CTAs (18 warps) per SM for the one- and two-tile
+// shapes, each with three 4 KiB slots per warp (192 KiB in flight per SM). Measured on the Llama
+// shapes at one token, graph-timed: three CTAs with two slots each run gate|up in the same 20.8 us
+// and 4096 x 4096 in 7.2 us against 6.2 us.
 template <int MT, int NS>
 struct StreamOcc {
-    static constexpr int kMinCtas = SPK_W4_MINCTAS;
+#ifdef SPK_STREAM_MINCTAS
+    static constexpr int kMinCtas = MT * NS <= 2 ? SPK_STREAM_MINCTAS : 1;
+#else
+    static constexpr int kMinCtas = MT * NS <= 2 ? 2 : 1;
+#endif
 };
 
+
 template <int MT, int NS, int CG, int ST, bool ASYM, bool DUAL>
-__global__ void __launch_bounds__(kStreamWarps * 32, StreamOcc<MT, NS>::kMinCtas)
+__global__ void __launch_bounds__(kStreamThreads, StreamOcc<MT, NS>::kMinCtas)
 w4_stream_kernel(const StreamParams p) {
     using S = Slot<NS, CG, ASYM>;
-    constexpr int NA = DUAL ? 2 : 1;
+    constexpr int NA = DUAL ? 2 : 1;  // accumulators a tile alternates between, so that consecutive MMAs do not depend on each other
     constexpr int kPitch = act_pitch(CG);
     constexpr int kActStages = ActRing<MT>::kStages;
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gl = lane >> 2, c = lane & 3;
+#ifdef SPK_W4_TRACE
+    int trace_n = 0;
+    unsigned grid_seq = 0;
+    if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 1024) grid_seq = atomicAdd(&g_w4s_seq[blockIdx.x], 1u);
+#endif
+    W4S_TRACE();  // 0: entry
+    W4S_GRID(0);
 
     // This CTA's range [f0, f1) of chunks, numbered super-strip major (G % CG == 0).
     const int chunks = p.G / CG;
@@ -256,59 +311,65 @@ w4_stream_kernel(const StreamParams p) {
 
     // shared memory: [8 warps][ST slots] codes+scales(+zeros) | act ring | barriers
     unsigned char* act_ring = smem + kStreamWarps * ST * S::kBytes;
-    const int act_stage = p.rows_max * kPitch;
-    uint64_t* bar_base = reinterpret_cast<uint64_t*>(act_ring + kActStages * (p.rows_max * kPitch));
-    uint64_t* a_full = bar_base;
-    uint64_t* a_empty = bar_base + kActStages;
-    uint64_t* bars = bar_base + 2 * kActStages + warp * ST;  // this warp's code ring (consumers only)
+    const int act_stage = act_stage_bytes(p.rows_max, CG);
+    uint64_t* bar_base = reinterpret_cast<uint64_t*>(act_ring + kActStages * act_stage);
+    uint64_t* a_landed = bar_base;              // [stages] the rows' bulk copies have landed
+    uint64_t* a_empty = bar_base + kActStages;  // [stages] the eight consumer warps are done with it
+    uint64_t* bars = bar_base + 2 * kActStages + (warp < kStreamWarps ? warp : 0) * ST;  // a consumer's code ring
 
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < kActStages; ++s) {
-            mbar_init(&a_full[s], 1);
+            mbar_init(&a_landed[s], 1);
             mbar_init(&a_empty[s], kStreamWarps);
         }
         ptx::fence_mbar_init();
     }
-    if (lane == 0) {
+    if (lane == 0 && warp < kStreamWarps) {
 #pragma unroll
         for (int s = 0; s < ST; ++s) mbar_init(&bars[s], 33);  // 1 expect_tx arrive + 32 cp.async arrives
         ptx::fence_mbar_init();
     }
     __syncthreads();  // the only block-wide barrier: barrier objects are ready
     pdl_release();  // a chained kernel behind this one may become resident as this grid's CTAs exit
+    W4S_TRACE();  // 1: set-up done
     if (n_chunks <= 0) return;
 
-    // ---- activation producer state (warp 0 only): chunk j goes to stage j % kActStages, one bulk
-    // copy per token row issued by lane r. It runs kActLead chunks ahead of warp 0's own
-    // consumption, which leaves the other warps kActStages - kActLead chunks of slack before
-    // warp 0 would have to wait for them.
-    constexpr int kActLead = kActStages > 4 ? kActStages - 3 : (kActStages > 2 ? kActStages - 1 : kActStages);
-    const unsigned char* a_row = reinterpret_cast<const unsigned char*>(p.A) +
-                                 static_cast<size_t>(tok0 + (lane < rows ? lane : 0)) * p.K * 2;
-    int a_issued = 0, a_ch = ch0, a_pstage = 0;
-    unsigned a_pphase = 0;
-    bool a_ok = true;
-    auto issue_acts = [&](int upto) {  // warp 0, all lanes
-        while (a_issued < upto && a_ok) {
-            if (a_issued >= kActStages) {
-                a_ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[a_pstage], a_pphase ^ 1u, p.status));
-                if (!a_ok) break;
-            }
-            if (lane == 0) mbar_arrive_expect_tx(&a_full[a_pstage], rows * (CG * 256));
+    // this lane's activation rows (token tiles mt); rows past the CTA's last re-read that one
+    int act_off[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        int r = 8 * mt + gl;
+        r = r < rows ? r : rows - 1;
+        act_off[mt] = r * kPitch + 16 * c;
+    }
+
+    if (warp == kStreamWarps) {
+        // ================= activation warp =================
+        // Chunk j goes to stage j % kActStages: one bulk copy per token row (lane r issues row r),
+        // signalled on the stage's barrier, which the consumers wait on. A stage is reused once the
+        // eight consumer warps have released it.
+        pdl_wait();  // the activations may be the output of the kernel in front of a chained launch
+        W4S_TRACE();  // act warp 2: predecessor complete
+        const unsigned char* a_row = reinterpret_cast<const unsigned char*>(p.A) +
+                                     static_cast<size_t>(tok0 + (lane < rows ? lane : 0)) * p.K * 2;
+        int i_ch = ch0, stage = 0;
+        unsigned phase = 0;
+        for (int j = 0; j < n_chunks; ++j) {
+            if (j >= kActStages && !__all_sync(0xffffffffu, mbar_wait(&a_empty[stage], phase ^ 1u, p.status))) break;
+            if (lane == 0) mbar_arrive_expect_tx(&a_landed[stage], rows * (CG * 256));
             __syncwarp();
             for (int r = lane; r < rows; r += 32)
-                bulk_g2s(act_ring + a_pstage * act_stage + r * kPitch,
-                         a_row + static_cast<size_t>(r - lane) * p.K * 2 + static_cast<size_t>(a_ch) * (CG * 256),
-                         CG * 256, &a_full[a_pstage]);
-            a_ch = a_ch + 1 == chunks ? 0 : a_ch + 1;
-            ++a_issued;
-            if (++a_pstage == kActStages) {
-                a_pstage = 0;
-                a_pphase ^= 1u;
-            }
+                bulk_g2s(act_ring + stage * act_stage + r * kPitch,
+                         a_row + static_cast<size_t>(r - lane) * p.K * 2 + static_cast<size_t>(i_ch) * (CG * 256), CG * 256,
+                         &a_landed[stage]);
+            i_ch = i_ch + 1 == chunks ? 0 : i_ch + 1;
+            if (++stage == kActStages) stage = 0, phase ^= 1u;
         }
-    };
+        return;  // copies still in flight complete on barriers the consumers wait on before they leave
+    }
+
+    // ================= consumer warps =================
     unsigned char* ring = smem + warp * (ST * S::kBytes);
     const size_t strip_bytes = static_cast<size_t>(p.G) * w4::kGroupBytes;
     auto valid_of = [&](int t_first) {
@@ -364,11 +425,13 @@ w4_stream_kernel(const StreamParams p) {
     };
 #pragma unroll 1
     for (int s = 0; s < ST; ++s) issue();
+    W4S_TRACE();  // 2: first copies requested
 
-    // The weight stream is under way; everything below reads activations or touches the output and the
-    // split-K scratch, which the kernel in front of a chained launch may still be using.
+    // The weight stream is under way; everything below touches the output and the split-K scratch, which
+    // the kernel in front of a chained launch may still be using.
     pdl_wait();
-    if (warp == 0) issue_acts(n_chunks < kActLead ? n_chunks : kActLead);
+    W4S_TRACE();  // 3: predecessor complete
+    W4S_GRID(1);
 
     // ---- consumer ----
     float acc[NS][MT][NA][4];
@@ -380,15 +443,6 @@ w4_stream_kernel(const StreamParams p) {
             for (int a = 0; a < NA; ++a)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[s][mt][a][e] = 0.f;
-
-    // this lane's activation rows (token tiles mt); rows past the CTA's last re-read that one
-    int act_off[MT];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        int r = 8 * mt + gl;
-        r = r < rows ? r : rows - 1;
-        act_off[mt] = r * kPitch + 16 * c;
-    }
 
     // Partial K segments this warp has added to the scratch: at most the first and the last of
     // its range. (first strip, chunks added); completed at the end of the kernel.
@@ -405,7 +459,7 @@ w4_stream_kernel(const StreamParams p) {
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    v[mt][e] = DUAL ? acc[s][mt][0][e] + acc[s][mt][NA - 1][e] : acc[s][mt][0][e];
+                    v[mt][e] = NA == 2 ? acc[s][mt][0][e] + acc[s][mt][NA - 1][e] : acc[s][mt][0][e];
 #pragma unroll
                     for (int a = 0; a < NA; ++a) acc[s][mt][a][e] = 0.f;
                 }
@@ -436,7 +490,7 @@ w4_stream_kernel(const StreamParams p) {
     int t_first = (ss0 * kStreamWarps + warp) * NS, valid = valid_of(t_first);
     unsigned phase = 0, a_phase = 0;
     for (int left = n_chunks; left > 0; --left) {
-        bool ok = mbar_wait(&a_full[a_stage], a_phase, p.status);
+        bool ok = mbar_wait(&a_landed[a_stage], a_phase, p.status);
         ok = __all_sync(0xffffffffu, ok && mbar_wait(&bars[slot_i], phase, p.status));
         if (!ok) {
             // Drain: give the copies already issued a bounded chance to land, then leave.
@@ -446,6 +500,7 @@ w4_stream_kernel(const StreamParams p) {
             }
             return;
         }
+        W4S_TRACE();  // 4 + 2 chunk: chunk and activations are in
         const unsigned char* slot = ring + slot_i * S::kBytes;
         const unsigned char* acts = act_ring + a_stage * act_stage;
 #pragma unroll
@@ -478,10 +533,7 @@ w4_stream_kernel(const StreamParams p) {
         __syncwarp();  // every lane has consumed both slots before they are handed back
         if (lane == 0) mbar_arrive(&a_empty[a_stage]);
         issue();
-        if (warp == 0) {
-            const int consumed = n_chunks - left + 1;
-            issue_acts(consumed + kActLead < n_chunks ? consumed + kActLead : n_chunks);
-        }
+        W4S_TRACE();  // 5 + 2 chunk: chunk consumed, next copy requested
         if (++slot_i == ST) {
             slot_i = 0;
             phase ^= 1u;
@@ -502,9 +554,12 @@ w4_stream_kernel(const StreamParams p) {
     }
 
     // ---- completion of the partial segments: one fence, then the per-strip counters ----
+    W4S_TRACE();  // loop done (all flushes issued)
+    W4S_GRID(2);
     if (n_pend == 0) return;
     __threadfence();
     __syncwarp();
+    W4S_TRACE();  // fence done
     for (int i = 0; i < n_pend; ++i) {
         const int nv = valid_of(pend_t[i]);
         for (int s = 0; s < nv; ++s) {
@@ -540,7 +595,24 @@ w4_stream_kernel(const StreamParams p) {
             }
         }
     }
+    W4S_TRACE();  // completion done
+    W4S_GRID(3);
 }
+
+#ifdef SPK_W4_TRACE
+}  // namespace
+}  // namespace spk
+extern "C" __attribute__((visibility("default"))) int spk_debug_w4s_trace(unsigned long long* buf) {
+    return cudaMemcpyToSymbol(spk::g_w4s_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+extern "C" __attribute__((visibility("default"))) int spk_debug_w4s_grid(unsigned long long* buf) {
+    static unsigned zeros[1024] = {};
+    if (cudaMemcpyToSymbol(spk::g_w4s_seq, zeros, sizeof(zeros)) != cudaSuccess) return 2;
+    return cudaMemcpyToSymbol(spk::g_w4s_grid, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+namespace spk {
+namespace {
+#endif
 
 // ---- host side --------------------------------------------------------------------------------------
 
@@ -548,6 +620,8 @@ w4_stream_kernel(const StreamParams p) {
 struct StreamTuning {
     int mt = 0, ns = 0, cg = 0, st = 0, ctas_per_sm = 0, min_units = 0;
 };
+
+constexpr int kDefaultCg = 4, kDefaultSt2 = 4;  // default chunk of the one- and two-tile shapes; slots of 2-group chunks
 
 StreamTuning read_tuning() {
     StreamTuning t;
@@ -561,14 +635,15 @@ int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target
                     const DeviceState& dev, cudaStream_t stream) {
     StreamParams p = base;
     auto kernel = w4_stream_kernel<MT, NS, CG, ST, ASYM, DUAL>;
-    constexpr int smem_max = stream_smem_bytes<ActRing<MT>::kStages, NS, CG, ST, ASYM>(8 * MT);
+    constexpr int smem_max = stream_smem_bytes<MT, NS, CG, ST, ASYM>(8 * MT);
+    if constexpr (smem_max > 227 * 1024) return fail(SPK_INVALID, "w4gemm: this stream kernel shape needs %d bytes of shared memory", smem_max);
     static bool configured[kMaxDevices] = {};
     if (!configured[dev.device]) {
         SPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
         configured[dev.device] = true;
     }
     p.rows_max = std::min(p.M, 8 * MT);
-    const int smem = stream_smem_bytes<ActRing<MT>::kStages, NS, CG, ST, ASYM>(p.rows_max);
+    const int smem = stream_smem_bytes<MT, NS, CG, ST, ASYM>(p.rows_max);
     p.super_strips = cdiv(p.T, kStreamWarps * NS);
     const int chunks = p.G / CG;
     const int m_chunks = cdiv(p.M, 8 * MT);
@@ -579,7 +654,7 @@ int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target
     static int occupancy[kMaxDevices][8 * MT + 1] = {};  // per device and activation-ring height
     int& occ = occupancy[dev.device][p.rows_max];
     if (occ == 0) {
-        SPK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kStreamWarps * 32, smem));
+        SPK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kStreamThreads, smem));
         if (occ < 1) return fail(SPK_CUDA_ERROR, "w4gemm: stream kernel does not fit an SM (smem %d)", smem);
     }
     int per_sm = occ;
@@ -590,14 +665,14 @@ int launch_stream_t(const StreamParams& base, bool whole, int ctas_per_sm_target
     const long long total = static_cast<long long>(p.super_strips) * chunks;
     const long long want = whole ? p.super_strips : std::max<long long>(1, total / std::max(1, min_chunks));
     const dim3 grid(static_cast<unsigned>(std::min(want, slots)), static_cast<unsigned>(m_chunks));
-    SPK_CUDA(launch_chained(kernel, grid, dim3(kStreamWarps * 32), smem, stream, p));
+    SPK_CUDA(launch_chained(kernel, grid, dim3(kStreamThreads), smem, stream, p));
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }
 
-// Block shapes, from sweeps on B200 (Llama-3-8B projections, CUDA-graph chained launches):
-//   M <= 8   one token tile, one strip per warp, 4-group chunks, 2 slots (8 KiB in flight per warp)
-//   M <= 16  two token tiles, same ring
+// Block shapes (Llama-3-8B projections, CUDA-graph chained launches on B200):
+//   M <= 8   one token tile, one strip per warp
+//   M <= 16  two token tiles
 //   M <= 32 / 64  four / eight token tiles on 2-group chunks (registers); these two are the
 //            warp-level-MMA fallback for shapes the tcgen05 path does not take
 // SPK_W4_CFG="mt,ns,cg,st[,ctas_per_sm[,min_chunks]]" overrides the rule for sweeps (0 = rule);
@@ -606,27 +681,32 @@ template <bool ASYM>
 int launch_stream(const StreamParams& p, bool whole, const DeviceState& dev, cudaStream_t stream) {
     static const StreamTuning tune = read_tuning();
     int mt = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
-    int ns = 1, cg = mt == 1 ? 4 : 2;
+    int ns = 1, cg = mt <= 2 ? kDefaultCg : 2;
     if (tune.mt > 0 && (p.M <= 8 * tune.mt || tune.mt == 8)) mt = tune.mt;
     if (tune.ns > 0) ns = tune.ns;
     if (tune.cg > 0) cg = tune.cg;
     if (mt >= 4) ns = 1, cg = std::min(cg, 2);
     while (cg > 1 && p.G % cg != 0) cg >>= 1;  // a chunk must not straddle a strip
-    int st = tune.st > 0 ? tune.st : (cg == 4 ? 2 : cg == 2 ? 4 : 8);
+    int st = tune.st > 0 ? tune.st : (cg == 4 ? 3 : cg == 2 ? (mt <= 2 ? kDefaultSt2 : 4) : 8);
     const bool dual = !whole && mt * ns <= 2;  // variant 3 keeps one accumulation chain for every M
     const int cap = tune.ctas_per_sm, min_chunks = tune.min_units > 0 ? tune.min_units : 1;
-#define SPK_W4_CASE(MT_, NS_, CG_, ST_)                                                                  \
-    if (mt == MT_ && ns == NS_ && cg == CG_ && st == ST_) {                                              \
+#define SPK_W4_CASE(MT_, NS_, CG_, ST_)                                                                       \
+    if (mt == MT_ && ns == NS_ && cg == CG_ && st == ST_) {                                                   \
         if (dual) return launch_stream_t<MT_, NS_, CG_, ST_, ASYM, (MT_ * NS_ <= 2)>(p, whole, cap, min_chunks, dev, stream); \
-        return launch_stream_t<MT_, NS_, CG_, ST_, ASYM, false>(p, whole, cap, min_chunks, dev, stream);  \
+        return launch_stream_t<MT_, NS_, CG_, ST_, ASYM, false>(p, whole, cap, min_chunks, dev, stream);      \
     }
     SPK_W4_CASE(1, 1, 1, 8)
+    SPK_W4_CASE(1, 1, 2, 3)
     SPK_W4_CASE(1, 1, 2, 4)
     SPK_W4_CASE(1, 1, 4, 2)
+    SPK_W4_CASE(1, 1, 4, 3)
+    SPK_W4_CASE(1, 1, 4, 4)
     SPK_W4_CASE(1, 2, 2, 2)
     SPK_W4_CASE(2, 1, 1, 8)
+    SPK_W4_CASE(2, 1, 2, 3)
     SPK_W4_CASE(2, 1, 2, 4)
     SPK_W4_CASE(2, 1, 4, 2)
+    SPK_W4_CASE(2, 1, 4, 3)
     SPK_W4_CASE(2, 2, 2, 2)
     SPK_W4_CASE(4, 1, 1, 8)
     SPK_W4_CASE(4, 1, 2, 4)

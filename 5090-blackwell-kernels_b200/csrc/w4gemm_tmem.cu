@@ -53,8 +53,24 @@ constexpr int kChunkGroups = 2;   // groups per chunk
 constexpr int kSets = 2;          // dequant warps per strip; set s takes chunks of parity s
 constexpr int DW = kStrips * kSets;
 constexpr int kChunkStages = 3;   // chunks of dequantized weights resident in TMEM
-constexpr int kCodeSlots = 3;     // per-warp ring of one-chunk code pieces
-constexpr int kActStages = 4;     // one group per slot
+// Ring depths. The activation tiles come from L2 through the same TMA queue as the weight stream, so a
+// tile requested when its slot frees arrives only after the weight copies queued in front of it
+// (measured ~1.9 us from request to use with 96 KiB of weight copies in flight per SM): the slots of
+// the activation ring divided by that round trip is a hard ceiling on groups per second, whatever the
+// dequant warps can do (4 slots held every token count to one chunk per ~1850 cycles). Hence a shallow
+// code ring (2 slots of 2 KiB per warp: 64 KiB per SM in flight, enough for the HBM rate) and as many
+// activation slots as shared memory allows (8 at 64 tokens, 16 below).
+#ifndef SPK_TMEM_CODE_SLOTS
+#define SPK_TMEM_CODE_SLOTS 2
+#endif
+#ifndef SPK_TMEM_ACT_BYTES
+#define SPK_TMEM_ACT_BYTES (128 * 1024)
+#endif
+constexpr int kCodeSlots = SPK_TMEM_CODE_SLOTS;  // per-warp ring of one-chunk code pieces
+template <int NT>
+constexpr int act_stages() {  // one group per slot
+    return SPK_TMEM_ACT_BYTES / (2 * NT * 128) > 16 ? 16 : SPK_TMEM_ACT_BYTES / (2 * NT * 128);
+}
 constexpr int kEpilogueWarp0 = DW, kMmaWarp = DW + 4, kProducerWarp0 = DW + 5;
 constexpr int kThreadsT = (DW + 6) * 32;
 constexpr int kTmemColsT = 512;
@@ -95,6 +111,7 @@ struct W4TmemSmem {
     static constexpr int kCodeRing = DW * kCodeSlots * kSlotBytes;
     static constexpr int kCodeArrivals = 1 + 2 * kChunkGroups + (ASYM ? kChunkGroups : 0);
     static constexpr int kBarriers = 1024;
+    static constexpr int kActStages = act_stages<NT>();
     static constexpr int kTotal = 1024 + kActStages * kActBytes + kCodeRing + kBarriers;
 };
 
@@ -130,9 +147,45 @@ __device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uin
         : "memory");
 }
 
+// The order in which a CTA visits the chunks [f0, f1) of its range. A range is up to three pieces: the
+// rest of the super-strip it starts in (a partial K segment), whole super-strips, and the beginning of
+// the super-strip it ends in (partial again). Partial segments end in reductions into the scratch and a
+// completion step whose latency is several round trips to L2; whole ones end in plain stores. The
+// partial pieces are therefore visited FIRST, so their completion overlaps the streaming of the rest,
+// and the last thing a CTA does is, whenever it owns a whole super-strip, a plain store.
+struct Visit {
+    int f0, h_end, t_start, lt, lh, n;
+    __device__ Visit(int f0_, int f1, int chunks) : f0(f0_), n(f1 - f0_) {
+        h_end = f0 % chunks == 0 ? f0 : min(f1, (f0 / chunks + 1) * chunks);
+        t_start = f1 % chunks == 0 ? f1 : max(h_end, (f1 / chunks) * chunks);
+        lt = f1 - t_start;
+        lh = h_end - f0;
+    }
+    __device__ __forceinline__ int at(int i) const { return i < lt ? t_start + i : (i < lt + lh ? f0 + (i - lt) : h_end + (i - lt - lh)); }
+    // the chunk visited i-th ends a K segment (the next one visited is not its successor in the same super-strip)
+    __device__ __forceinline__ bool ends_segment(int i, int ch, int chunks) const {
+        return ch == chunks - 1 || i == n - 1 || i == lt - 1 || i == lt + lh - 1;
+    }
+};
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+// D[tmem] += A[tmem] * B[smem] (accumulating form: the predicate is a constant)
+__device__ __forceinline__ void mma_f16_ta_acc(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc)
+        : "memory");
+}
+
 template <int NT, bool ASYM>
 __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_constant__ CUtensorMap map_act, const W4TmemParams p) {
     using L = W4TmemSmem<NT, ASYM>;
+    constexpr int kActStages = L::kActStages;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
     unsigned char* acts = base;
@@ -158,7 +211,8 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     const long long total = static_cast<long long>(p.super_strips) * chunks;
     const int f0 = static_cast<int>(blockIdx.x * total / gridDim.x);
     const int f1 = static_cast<int>((blockIdx.x + 1) * total / gridDim.x);
-    const int n_chunks = f1 - f0;
+    const Visit visit(f0, f1, chunks);
+    const int n_chunks = visit.n;
 
     // barrier set-up spread over lanes: every dequant warp its own code barriers, one epilogue warp the rest
     if (warp < DW) {
@@ -197,13 +251,13 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         const uint32_t my_tmem = tmem_base + (static_cast<uint32_t>(16 * strip) << 16) + kWeightCol0;
         unsigned char* ring = codes + warp * (kCodeSlots * L::kSlotBytes);
         uint64_t* my_bar = code_bar + warp * kCodeSlots;
-        // next chunk to fetch: this warp takes chunks f0 + set, f0 + set + 2, ...
-        int pf = f0 + set, p_slot = 0, p_ss = pf / chunks, p_ch = pf - p_ss * chunks;
-        int n_issued = 0;
+        // next chunk to fetch: this warp takes the chunks visited set-th, (set + 2)-th, ...
+        int pi = set, p_slot = 0, n_issued = 0;
         auto issue = [&]() {
-            if (pf >= f1) return;
+            if (pi >= n_chunks) return;
             ++n_issued;
-            const int t = p_ss * kStrips + strip, g0 = p_ch * kChunkGroups;
+            const int f = visit.at(pi), ss = f / chunks, ch = f - ss * chunks;
+            const int t = ss * kStrips + strip, g0 = ch * kChunkGroups;
             unsigned char* slot = ring + p_slot * L::kSlotBytes;
             uint64_t* bar = &my_bar[p_slot];
             if (lane == 0) {
@@ -219,15 +273,13 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 cp_async16_t(slot + L::kCodeBytes + kChunkGroups * 32 + j * 16, p.zeros + static_cast<size_t>(g0 + j) * p.N + 16 * t);
                 cp_async_arrive_t(bar);
             }
-            pf += kSets;
-            p_ch += kSets;
-            while (p_ch >= chunks) p_ch -= chunks, ++p_ss;
+            pi += kSets;
             p_slot = p_slot + 1 == kCodeSlots ? 0 : p_slot + 1;
         };
         for (int i = 0; i < kCodeSlots; ++i) issue();
 
         const int n_mine = n_chunks > set ? (n_chunks - set + 1) / 2 : 0;
-        int slot_i = 0, cs = set;  // chunk stage of local chunk index set, set + 2, ...
+        int slot_i = 0, cs = set;  // chunk stage of the chunks visited set-th, (set + 2)-th, ...
         unsigned code_ph = 0, ph = 0;
         bool ok = true, chained = false;
         int it = 0;
@@ -309,10 +361,11 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     } else if (warp == kProducerWarp0) {
         // ================= activation producer: one 128-k group (two units) per slot =================
         pdl_wait();  // the re-ordered activations are written by the kernel in front of this one
-        int s = 0, ch = f0 % chunks;
+        int s = 0;
         unsigned ph = 0;
         bool ok = true;
-        for (int f = f0; f < f1 && ok; ++f) {
+        for (int i = 0; i < n_chunks && ok; ++i) {
+            const int ch = visit.at(i) % chunks;
             for (int sub = 0; sub < kChunkGroups && ok; ++sub) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&act_empty[s], ph ^ 1u, p.status));
                 if (!ok) break;
@@ -325,19 +378,23 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 __syncwarp();
                 if (++s == kActStages) s = 0, ph ^= 1u;
             }
-            if (++ch == chunks) ch = 0;
         }
     } else if (warp == kMmaWarp) {
         // ================= MMA issuer: the loop runs warp-wide, one elected lane issues =================
+        // This warp shares its scheduler with four dequant warps that always have work, so every
+        // instruction here costs several cycles of the critical path: descriptors are built once and
+        // advanced with 32-bit adds, and only the first MMA of a K segment carries a run-time predicate.
         constexpr uint32_t idesc = umma::instr_desc(128, NT, 1, 1);  // bf16 x bf16 -> f32
         const uint64_t bdesc0 = umma::smem_desc_k128(acts);
-        int seg = 0, cs = 0, as = 0, ch = f0 % chunks;
+        const uint32_t bd_lo0 = static_cast<uint32_t>(bdesc0), bd_hi = static_cast<uint32_t>(bdesc0 >> 32);
+        int seg = 0, cs = 0, as = 0;
         unsigned ph = 0, aph = 0;
         bool ok = true, fresh = true;
         // Everything this warp waits for needs the activations, which the producer requests only after the
         // kernel in front of a chained launch has completed; its bounded waits start counting from there.
         pdl_wait();
-        for (int f = f0; f < f1 && ok; ++f) {
+        for (int i = 0; i < n_chunks && ok; ++i) {
+            const int ch = visit.at(i) % chunks;
             const int buf = seg & 1;
             if (fresh) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&acc_free[buf], ((seg >> 1) & 1) ^ 1, p.status));
@@ -348,27 +405,31 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             ok = __all_sync(0xffffffffu, mbar_wait(&a_ready[cs], ph, p.status));
             if (!ok) break;
             W4_TRACE();  // + 1: weights ready
-            for (int sub = 0; sub < kChunkGroups && ok; ++sub) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&act_full[as], aph, p.status));
-                if (!ok) break;
-                umma::fence_after_sync();
-                const uint64_t bd = bdesc0 + static_cast<uint64_t>(as) * (L::kActBytes >> 4);
-                const uint32_t wa = tmem_base + kWeightCol0 + cs * 128 + sub * 64;
-                if (umma::elect_one()) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
+            for (int sub = 0; sub < kChunkGroups; ++sub) {
+                ok = ok && __all_sync(0xffffffffu, mbar_wait(&act_full[as], aph, p.status));
+                if (ok) {
+                    umma::fence_after_sync();
+                    const uint32_t bd = bd_lo0 + static_cast<uint32_t>(as) * (L::kActBytes >> 4);
+                    const uint32_t wa = tmem_base + kWeightCol0 + cs * 128 + sub * 64;
+                    if (umma::elect_one()) {
+                        if (sub == 0)
+                            mma_f16_ta(acc, wa, make_desc(bd, bd_hi), idesc, !fresh);
+                        else
+                            mma_f16_ta_acc(acc, wa, make_desc(bd, bd_hi), idesc);
 #pragma unroll
-                        for (int r = 0; r < 4; ++r)
-                            mma_f16_ta(acc, wa + h * 32 + r * 8, bd + h * (NT * 128 >> 4) + 2 * r, idesc,
-                                       !fresh || sub > 0 || h > 0 || r > 0);
-                    umma::mma_commit(&act_empty[as]);
+                        for (int hr = 1; hr < 8; ++hr)
+                            mma_f16_ta_acc(acc, wa + (hr >> 2) * 32 + (hr & 3) * 8,
+                                           make_desc(bd + (hr >> 2) * (NT * 128 >> 4) + 2 * (hr & 3), bd_hi), idesc);
+                        umma::mma_commit(&act_empty[as]);
+                    }
+                    __syncwarp();
+                    if (++as == kActStages) as = 0, aph ^= 1u;
                 }
-                __syncwarp();
-                if (++as == kActStages) as = 0, aph ^= 1u;
             }
             if (!ok) break;
             fresh = false;
-            const bool seg_end = ch == chunks - 1 || f == f1 - 1;
+            const bool seg_end = visit.ends_segment(i, ch, chunks);
             if (umma::elect_one()) {
                 umma::mma_commit(&a_free[cs]);
                 if (seg_end) umma::mma_commit(&acc_ready[buf]);
@@ -376,7 +437,6 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             __syncwarp();
             if (++cs == kChunkStages) cs = 0, ph ^= 1u;
             if (seg_end) ++seg, fresh = true;
-            if (++ch == chunks) ch = 0;
         }
         if (!ok) {
             // MMAs already issued may still be reading TMEM and shared memory: one more commit, and a
@@ -389,12 +449,12 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         // ================= epilogue warps: TMEM lane quarter = warp % 4 =================
         const int quarter = warp & 3;
         pdl_wait();  // C and the split-K scratch may still be in use by the kernels in front
-        int pend_ss[2] = {0, 0}, pend_n[2] = {0, 0}, n_pend = 0;
-        int seg = 0, seg_ch0 = f0 % chunks;
+        int seg = 0, seg_ch0 = -1;
         bool ok = true;
-        for (int f = f0; f < f1 && ok; ++f) {
-            const int ss = f / chunks, ch = f - ss * chunks;
-            if (!(ch == chunks - 1 || f == f1 - 1)) continue;
+        for (int i = 0; i < n_chunks && ok; ++i) {
+            const int f = visit.at(i), ss = f / chunks, ch = f - ss * chunks;
+            if (seg_ch0 < 0) seg_ch0 = ch;
+            if (!visit.ends_segment(i, ch, chunks)) continue;
             const int buf = seg & 1;
             W4_TRACE();  // epilogue 2 + 3 seg: waiting for a segment
             ok = __all_sync(0xffffffffu, mbar_wait(&acc_ready[buf], (seg >> 1) & 1, p.status));
@@ -407,15 +467,15 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 uint32_t r[16];
                 umma::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * NT + c0, r);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[c0 + i] = r[i];
+                for (int j = 0; j < 16; ++j) v[c0 + j] = r[j];
             }
             umma::tmem_ld_wait();
             umma::fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_free[buf]);
             const int n = ss * 128 + quarter * 32 + lane;  // TMEM lane = column of the super-strip
-            const bool whole_k = seg_ch0 == 0 && ch == chunks - 1;
-            if (whole_k) {
+            const int seg_chunks = ch - seg_ch0 + 1;
+            if (seg_chunks == chunks) {
 #pragma unroll
                 for (int t = 0; t < NT; ++t)
                     if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[t]));
@@ -423,37 +483,23 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 // The scratch of this kernel is [32-column block][NT / 4][lane][4 tokens]: a lane's partial sums go
                 // out as NT / 4 vector reductions and a warp's reduction covers 512 contiguous bytes (a scalar
                 // reduction per token row cost ~100 cycles each here).
-                float* mine = p.partials + (static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane) * 4;
+                float4* mine = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane;
 #pragma unroll
                 for (int t = 0; t < NT; t += 4)
                     if (t < p.M)
-                        red_add_v4(mine + t * 32, __uint_as_float(v[t]), __uint_as_float(v[t + 1]), __uint_as_float(v[t + 2]),
-                                   __uint_as_float(v[t + 3]));
-            }
-            if (!whole_k) {
-                pend_ss[n_pend] = ss;
-                pend_n[n_pend] = ch - seg_ch0 + 1;
-                ++n_pend;
-            }
-            ++seg;
-            seg_ch0 = 0;
-            W4_TRACE();  // + 2: stored or reduced
-        }
-        W4_TRACE();  // before completion
-        // completion of the partial segments: one fence, then the per-(tile, quarter) counters
-        if (n_pend > 0) {
-            __threadfence();
-            __syncwarp();
-            for (int i = 0; i < n_pend; ++i) {
+                        red_add_v4(reinterpret_cast<float*>(mine + (t / 4) * 32), __uint_as_float(v[t]), __uint_as_float(v[t + 1]),
+                                   __uint_as_float(v[t + 2]), __uint_as_float(v[t + 3]));
+                // Completion right away (this warp has nothing else to do until the next segment ends): one fence,
+                // then the per-(super-strip, quarter) counter; whoever brings it to `chunks` owns the sums.
+                __threadfence();
+                __syncwarp();
                 unsigned done = 0;
-                unsigned* counter = p.counters + pend_ss[i] * 4 + quarter;
-                if (lane == 0) done = atomicAdd(counter, static_cast<unsigned>(pend_n[i]));
+                unsigned* counter = p.counters + ss * 4 + quarter;
+                if (lane == 0) done = atomicAdd(counter, static_cast<unsigned>(seg_chunks));
                 done = __shfl_sync(0xffffffffu, done, 0);
-                if (done + static_cast<unsigned>(pend_n[i]) == static_cast<unsigned>(chunks)) {
+                if (done + static_cast<unsigned>(seg_chunks) == static_cast<unsigned>(chunks)) {
                     __threadfence();
-                    const int n = pend_ss[i] * 128 + quarter * 32 + lane;
                     // this lane's NT sums: NT / 4 vector loads in one round trip, re-zero, store bf16
-                    float4* mine = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane;
                     float4 w[NT / 4];
 #pragma unroll
                     for (int j = 0; j < NT / 4; ++j) w[j] = 4 * j < p.M ? __ldcg(mine + j * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -470,6 +516,9 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                     if (lane == 0) *counter = 0u;
                 }
             }
+            ++seg;
+            seg_ch0 = -1;
+            W4_TRACE();  // + 2: stored or reduced and completed
         }
     }
     W4_TRACE();  // role finished
