@@ -4,6 +4,7 @@
 //   kFp8Mx   e4m3 x e4m3, ue8m0 scale per 32 k           kind::mxf8f6f4.block_scale
 //   kNvfp4   e2m1 x e2m1, e4m3 scale per 16 k            kind::mxf4nvf4.block_scale.scale_vec::4X
 //   kMxfp4   e2m1 x e2m1, ue8m0 scale per 32 k           kind::mxf4nvf4.block_scale.scale_vec::2X
+//   kBf16    bf16 x bf16 (the prefill route of the int4 GEMM: activations times dequantized weights)   kind::f16
 //
 // A persistent CTA computes 128 x BN tiles of C one after another. Roles, one warp each unless noted:
 //   warp 0   producer: per K block (128 bytes of K per row) one thread issues two tiled TMA loads
@@ -35,7 +36,7 @@ using ptx::mbar_arrive_expect_tx;
 using ptx::mbar_init;
 using ptx::mbar_wait;
 
-enum UmmaMode { kFp8 = 0, kFp8Mx = 1, kNvfp4 = 2, kMxfp4 = 3 };
+enum UmmaMode { kFp8 = 0, kFp8Mx = 1, kNvfp4 = 2, kMxfp4 = 3, kBf16 = 4 };
 
 constexpr int kBM = 128, kBKBytes = 128;
 constexpr int kSfTile = 512;             // 128 rows x 4 scale bytes
@@ -56,11 +57,12 @@ __device__ __forceinline__ void grouped_tile(int tiles_m, int tiles_n, int bid, 
 
 template <int MODE>
 struct ModeTraits {
-    static constexpr bool kScaled = MODE != kFp8;
+    static constexpr bool kScaled = MODE != kFp8 && MODE != kBf16;
     // scale tiles per 128-row block per stage: MXFP8 1 (4 scales = 128 k), NVFP4 4 (one per MMA),
     // MXFP4 2 (one per two MMAs)
     static constexpr int kTiles = MODE == kFp8Mx ? 1 : MODE == kNvfp4 ? 4 : MODE == kMxfp4 ? 2 : 0;
     static constexpr int kElemsPerByte = (MODE == kNvfp4 || MODE == kMxfp4) ? 2 : 1;
+    static constexpr int kBytesPerElem = MODE == kBf16 ? 2 : 1;  // K in elements -> bytes: K * kBytesPerElem / kElemsPerByte
 };
 
 template <int BN, int MODE>
@@ -73,7 +75,7 @@ struct UmmaCfg {
     // Per-tensor fp8 runs two CTAs per SM with two stages each: one CTA's epilogue (TMEM -> bf16
     // stores) and prologue then overlap the other's MMAs. The block-scaled modes need their TMEM
     // columns for scales and keep one CTA per SM with four stages.
-    static constexpr int kCtasPerSm = (MODE == kFp8 && UMMA_FP8_TWO_CTAS) ? 2 : 1;
+    static constexpr int kCtasPerSm = ((MODE == kFp8 || MODE == kBf16) && UMMA_FP8_TWO_CTAS) ? 2 : 1;
     static constexpr int kStages = kCtasPerSm == 2 ? 2 : 4;
     static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int kTmemCols = T::kScaled ? 512 : BN;
@@ -156,7 +158,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
     const int total_tiles = tiles_m * tiles_n;
-    const int k_bytes = p.K / T::kElemsPerByte;
+    const int k_bytes = p.K * T::kBytesPerElem / T::kElemsPerByte;
     const int k_blocks = (k_bytes + kBKBytes - 1) / kBKBytes;
 
     if (threadIdx.x == 0) {
@@ -227,7 +229,13 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (umma::elect_one()) {
                     const unsigned char* st = tiles + s * Cfg::kStageBytes;
                     const uint64_t adesc = umma::smem_desc_k128(st), bdesc = umma::smem_desc_k128(st + Cfg::kABytes);
-                    if (!T::kScaled) {
+                    if (MODE == kBf16) {
+                        constexpr uint32_t idesc = umma::instr_desc(kBM, BN, 1, 1);  // bf16 x bf16 -> f32, K = 16 per MMA
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma::mma_f16(tmem_acc, umma::desc_advance(adesc, 32 * k), umma::desc_advance(bdesc, 32 * k), idesc,
+                                          kb > 0 || k > 0);
+                    } else if (!T::kScaled) {
                         constexpr uint32_t idesc = umma::instr_desc(kBM, BN, 0, 0);  // e4m3 x e4m3 -> f32
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
@@ -319,7 +327,7 @@ int launch_umma(const simt::Params& q, const unsigned char* sfa, const unsigned 
     using T = ModeTraits<MODE>;
     static_assert(Cfg::kStageBytes % 1024 == 0, "stages must keep the 1024-byte tile alignment");
     static_assert(Cfg::kSmem <= 227 * 1024, "stage ring exceeds shared memory");
-    const uint64_t row_bytes = static_cast<uint64_t>(q.K) / T::kElemsPerByte;
+    const uint64_t row_bytes = static_cast<uint64_t>(q.K) * T::kBytesPerElem / T::kElemsPerByte;
     CUtensorMap map_a, map_b;
     if (!umma::make_map_2d_u8(&map_a, q.A, row_bytes, static_cast<uint64_t>(q.M), kBM) ||
         !umma::make_map_2d_u8(&map_b, q.Bt, row_bytes, static_cast<uint64_t>(q.N), BN))
@@ -396,7 +404,7 @@ qgemm_umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     pdl_release();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x % p.n_tiles, sk = blockIdx.x / p.n_tiles;
-    const int k_bytes = p.K / T::kElemsPerByte;
+    const int k_bytes = p.K * T::kBytesPerElem / T::kElemsPerByte;
     const int k_blocks_all = (k_bytes + kBKBytes - 1) / kBKBytes;
     const int kb0 = static_cast<int>(static_cast<long long>(sk) * k_blocks_all / p.split);
     const int kb1 = static_cast<int>(static_cast<long long>(sk + 1) * k_blocks_all / p.split);
@@ -573,7 +581,7 @@ int launch_decode(const simt::Params& q, const unsigned char* sfw, const unsigne
     using Cfg = DecodeCfg<NT, MODE>;
     using T = ModeTraits<MODE>;
     static_assert(Cfg::kSmem <= 227 * 1024, "stage ring exceeds shared memory");
-    const uint64_t row_bytes = static_cast<uint64_t>(q.K) / T::kElemsPerByte;
+    const uint64_t row_bytes = static_cast<uint64_t>(q.K) * T::kBytesPerElem / T::kElemsPerByte;
     CUtensorMap map_w, map_x;
     if (!umma::make_map_2d_u8(&map_w, q.Bt, row_bytes, static_cast<uint64_t>(q.N), kBM) ||
         !umma::make_map_2d_u8(&map_x, q.A, row_bytes, static_cast<uint64_t>(q.M), NT))
@@ -879,6 +887,20 @@ int fp8gemm_umma_try(const simt::Params& p, bool mx, int variant, cudaStream_t s
     // the scratch is shared with the split-K kernels, which expect it zeroed
     SPK_CUDA(cudaMemsetAsync(sfa, 0, a_bytes + b_bytes, stream));
     return SPK_OK;
+}
+
+// C bf16 [M][N] = A bf16 [M][K] * Bt bf16 [N][K]^T on the tile kernel (the second half of the int4 prefill route).
+// Needs N % 64 == 0, K % 8 == 0 and 16-byte aligned operands and output.
+int bf16gemm_umma(const void* A, const void* Bt, void* C, int M, int N, int K, cudaStream_t stream) {
+    DeviceState* dev = nullptr;
+    if (int rc = device_state(&dev)) return rc;
+    simt::Params p{};
+    p.A = static_cast<const unsigned char*>(A);
+    p.Bt = static_cast<const unsigned char*>(Bt);
+    p.C = static_cast<__nv_bfloat16*>(C);
+    p.M = M, p.N = N, p.K = K;
+    return wide_tiles(M, N, dev->sm_count) ? launch_umma<256, kBf16>(p, nullptr, nullptr, dev, stream)
+                                           : launch_umma<128, kBf16>(p, nullptr, nullptr, dev, stream);
 }
 
 // fp4gemm on the tensor cores: variants 1 and 2 at every M > 64 (TMA zero-fills the rows past M and the

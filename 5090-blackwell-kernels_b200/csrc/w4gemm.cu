@@ -5,7 +5,9 @@
 //      reference's w4_naive_kernel, src/kernels/w4gemm.cu:46-67)
 //   1  one warp per 16-column strip and 8 tokens, codes and activations straight from global
 //      memory into registers, register dequant, warp-level MMA
-//   2  the B200 weight stream (default): every warp owns a private ring of bulk asynchronous
+//   2  (default) by token count: up to 16 tokens the B200 weight stream described next, up to a few hundred
+//      the tcgen05 kernel with the weights in TMEM (w4gemm_tmem.cu), above that dequantize once + dense
+//      bf16 tcgen05 GEMM (w4_prefill.cu). The weight stream: every warp owns a private ring of bulk asynchronous
 //      copies (TMA engine) that brings whole 1 KiB groups of codes plus their scales into
 //      shared memory; the (strips x groups) work is cut into equal contiguous ranges, one per
 //      CTA, so all SMs stream the same number of bytes; a strip whose K is shared by two CTAs
@@ -723,6 +725,9 @@ namespace spk {
 // defined in w4gemm_tmem.cu
 int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
                     int K, cudaStream_t stream, bool* taken);
+// defined in w4_prefill.cu
+int w4gemm_prefill_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
+                       int K, cudaStream_t stream, bool* taken);
 // defined in w4gemm_umma.cu
 int w4gemm_umma_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
                     int K, cudaStream_t stream, bool* taken);
@@ -764,8 +769,10 @@ extern "C" int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void*
         SPK_CHECK_LAUNCH();
         return SPK_OK;
     }
-    if (variant == 2) {  // the tensor-core route for mid-size token counts
+    if (variant == 2) {  // the tensor-core routes: dense bf16 GEMM on dequantized weights for many tokens, TMEM weights for few
         bool taken = false;
+        const int rcp = w4gemm_prefill_try(A, packed, scales, zeros, C, M, N, K, stream, &taken);
+        if (taken || rcp != SPK_OK) return rcp;
         const int rc0 = w4gemm_tmem_try(A, packed, scales, zeros, C, M, N, K, stream, &taken);
         if (taken || rc0 != SPK_OK) return rc0;
         const int rc = w4gemm_umma_try(A, packed, scales, zeros, C, M, N, K, stream, &taken);

@@ -48,6 +48,7 @@ _spk_w4_quantize = _sig("spk_w4_quantize_bf16", [_p, _p, _p, _p, _i, _i, _p])
 _spk_w4_repack = _sig("spk_w4_repack", [_p, _p, _i, _i, _p])
 _spk_w4gemm = _sig("spk_w4gemm_bf16", [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
 _spk_w4gemm_noalloc = _sig("spk_w4gemm_bf16_noalloc", [_p, _p, _p, _p, _p, _i, _i, _i, _p])
+_spk_w4_prefill_reserve = _sig("spk_w4_prefill_reserve", [ctypes.c_longlong])
 _spk_w4gemm_noalloc_status = _sig("spk_w4gemm_noalloc_status", [_p, ctypes.POINTER(_i)])
 _spk_debug_expire_wait = _sig("spk_debug_expire_wait", [_i, _p])
 _sig("spk_w4gemm_num_variants", [])
@@ -225,6 +226,13 @@ def w4gemm_noalloc(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
         _status(_spk_w4gemm_noalloc(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros),
                                     out.data_ptr(), M, N, K, _stream(a)))
     return out
+
+
+def w4_prefill_reserve(nbytes: int, device=None) -> None:
+    """Size the bf16 scratch of the many-token route of w4gemm (N * K * 2 bytes of the largest weight) now,
+    e.g. before capturing a CUDA graph."""
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _status(_spk_w4_prefill_reserve(int(nbytes)))
 
 
 def w4gemm_noalloc_status(device=None) -> int:
@@ -554,6 +562,7 @@ _sig("spk_comm_open", [ctypes.c_char_p, ctypes.POINTER(_p)])
 _sig("spk_comm_close", [_p])
 _sig("spk_comm_status", [_p, ctypes.POINTER(_i)])
 _sig("spk_allreduce_push_bf16", [_p, ctypes.c_longlong, ctypes.POINTER(_p), _i, _i, ctypes.c_longlong, _p])
+_sig("spk_allreduce_push_bf16_mode", [_p, ctypes.c_longlong, ctypes.POINTER(_p), _i, _i, ctypes.c_longlong, _i, _p])
 
 
 def comm_alloc(world: int, slot_elems: int) -> int:
@@ -592,11 +601,12 @@ def comm_status(local_ptr: int) -> int:
     return code.value
 
 
-def allreduce_push(t: torch.Tensor, ptrs, rank: int, slot_elems: int) -> torch.Tensor:
-    """In-place sum of the contiguous bf16 tensor t over the ranks whose buffers are `ptrs`."""
+def allreduce_push(t: torch.Tensor, ptrs, rank: int, slot_elems: int, mode: int = 0) -> torch.Tensor:
+    """In-place sum of the contiguous bf16 tensor t over the ranks whose buffers are `ptrs`.
+    mode 0: the library picks the form, 1: one phase, 2: two phases (reduce-scatter + all-gather)."""
     _check_cuda_contig(t, "t")
     _check(t.dtype == torch.bfloat16, "allreduce_push: bf16 only")
     arr = (_p * len(ptrs))(*ptrs)
     with torch.cuda.device(t.device):
-        _status(_lib.spk_allreduce_push_bf16(t.data_ptr(), t.numel(), arr, rank, len(ptrs), slot_elems, _stream(t)))
+        _status(_lib.spk_allreduce_push_bf16_mode(t.data_ptr(), t.numel(), arr, rank, len(ptrs), slot_elems, int(mode), _stream(t)))
     return t

@@ -176,8 +176,10 @@ class PushAllReduce:
                 pass
         self.local, self.ptrs = 0, []
 
-    def __call__(self, t: torch.Tensor) -> torch.Tensor:
-        return self._C.allreduce_push(t, self.ptrs, self.rank, self.slot_elems)
+    def __call__(self, t: torch.Tensor, mode: int = 0) -> torch.Tensor:
+        """mode 0: the library picks one phase (every rank stores its tensor into every peer) or two
+        (reduce-scatter + all-gather by peer stores, for large tensors on four ranks and more); 1 / 2 force one."""
+        return self._C.allreduce_push(t, self.ptrs, self.rank, self.slot_elems, mode)
 
     def status(self) -> int:
         """0, or the status a bounded wait for a peer left behind (synchronizes the device)."""

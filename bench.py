@@ -47,7 +47,6 @@ LAYERS = 16
 WORKLOAD = "llama3_8b_mlp_int4_decode"
 STACK_WORKLOAD = "llama3_8b_projection_stack_int4_decode"
 FALLBACK_HBM_GBS = 6650.0
-PUSH_MAX_BYTES = 128 << 10  # all-reduce payloads up to this size go by peer stores
 
 
 def alg_bytes(M: int, N: int, K: int) -> int:
@@ -266,15 +265,14 @@ def run_ours(args) -> None:
                 from spark_kernels import tp as tpmod_
 
                 pusher = tpmod_.PushAllReduce(sk, None, 64 * HIDDEN, dev)
-                # one hop of peer stores wins while the sum is latency bound; from 256 KiB up every rank
-                # would push world x the tensor, and NCCL's in-switch reduction is faster (measured at tp8:
-                # 8 KiB 13.6 us per GEMM+sum against 19.6, 128 KiB 21.4 against 24.4, 512 KiB 36.8 against 29.2)
-                push_max = PUSH_MAX_BYTES
+                # One kernel per rank, peer stores over NVLink: one hop (every rank stores its tensor into every
+                # peer) while the sum is latency bound, reduce-scatter + all-gather (two hops, 2 (world - 1) / world
+                # of the tensor per rank) for large tensors on four ranks and more; the library picks.
 
                 def reduce(t, _p=pusher):
-                    return _p(t) if t.numel() * t.element_size() <= push_max else dist.all_reduce(t)
+                    return _p(t)
 
-                reduce_name = f"push up to {push_max >> 10} KiB (peer stores over NVLink, one kernel per rank), nccl above"
+                reduce_name = "push (peer stores over NVLink, one kernel per rank; two-phase from 4 ranks and 128 KiB up)"
             except Exception as e:  # CUDA IPC can be closed to a container; NCCL then carries the sum
                 reduce_name = f"nccl (push unavailable: {type(e).__name__})"
             ok_all = torch.tensor([1.0 if reduce_name.startswith("push") else 0.0], device=dev)
@@ -561,7 +559,7 @@ def run_ours(args) -> None:
                 "mlp": {"value": round(value, 2), "unit": "GB/s", "ms_per_step": round(ms_total / args.steps, 4),
                         "e2e": round(e2e, 2), "config": mlp_cfg, "roofline": mlp_roofline},
                 "secondary": None,
-                "gpu_launches": (2 * launches_per_pass + (2 * 32 if reduce_name.startswith("push") and 64 * HIDDEN * 2 <= PUSH_MAX_BYTES else 0)) * args.steps,
+                "gpu_launches": (2 * launches_per_pass + (2 * 32 if reduce_name.startswith("push") else 0)) * args.steps,
                 "clocks": clocks,
             }
         print(json.dumps(line), flush=True)

@@ -85,6 +85,11 @@ SPK_API int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, const 
  * clears it, without allocating. A GEMM call does not clear the word, so a timeout stays visible
  * until it is read here. */
 SPK_API int spk_w4gemm_noalloc_status(void* stream, int* code);
+/* No counterpart in the reference (its workspaces grow inside the launchers). From 256 tokens up variant 2
+ * dequantizes the weight once into a per-device bf16 scratch of N * K * 2 bytes and runs a dense GEMM; the
+ * scratch grows on demand with cudaMalloc. Call this with the largest N * K * 2 you will use before
+ * capturing a CUDA graph so that no allocation happens during capture. */
+SPK_API int spk_w4_prefill_reserve(long long bytes);
 /* reference include/spark/kernels.h:414-416 */
 SPK_API int spk_w4gemm_num_variants(void);
 SPK_API int spk_w4gemm_default_variant(void);
@@ -197,6 +202,13 @@ SPK_API int spk_comm_close(void* ptr);
 SPK_API int spk_comm_status(void* local_buf, int* code);
 SPK_API int spk_allreduce_push_bf16(void* data, long long n, void* const* bufs, int rank, int world,
                                     long long slot_elems, void* stream);
+/* The same sum with the form forced: mode 1 one phase (every rank stores its whole tensor into every
+ * peer), mode 2 two phases (reduce-scatter then all-gather by peer stores and arrival counters), mode 3
+ * the two phases with the sequence number travelling inside every 8-byte store (no fence, no counter:
+ * the lowest latency), mode 0 what spk_allreduce_push_bf16 picks. Modes 2 and 3 need n % (8 world) == 0.
+ * Identical bits on every rank in all forms; they may be mixed as long as all ranks make the same calls. */
+SPK_API int spk_allreduce_push_bf16_mode(void* data, long long n, void* const* bufs, int rank, int world,
+                                         long long slot_elems, int mode, void* stream);
 
 #ifdef __cplusplus
 }

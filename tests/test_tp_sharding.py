@@ -113,7 +113,7 @@ class _FakeComm:
     def comm_status(self, ptr):
         return 0
 
-    def allreduce_push(self, t, ptrs, rank, slot_elems):
+    def allreduce_push(self, t, ptrs, rank, slot_elems, mode=0):
         self.calls.append((tuple(ptrs), rank, slot_elems))
         return t
 

@@ -228,3 +228,30 @@ def test_an_expired_wait_is_reported_and_the_scratch_is_clean_again(sk, orc):
                           f"after an expired wait, M={M}")
     assert_bf16_close(sk.w4gemm(a, ww, variant=2), want, "after an expired wait")
     assert sk._C.device_status() == 0
+
+
+@pytest.mark.parametrize("asym", [False, True], ids=["sym", "asym"])
+@pytest.mark.parametrize("M,K,N", [(256, 1152, 256), (300, 256, 192), (513, 512, 4096), (2048, 4096, 4096), (640, 256, 4160)])
+def test_w4gemm_many_tokens_matches_oracle(sk, orc, M, K, N, asym):
+    """From 256 tokens up the default variant dequantizes the weight once (bit-exact bf16((q - z) * s)) and runs
+    a dense bf16 tensor-core GEMM. Checked on sampled rows over all columns at the large shape (a row of C
+    depends on one row of A only), on everything below."""
+    ww = sk.W4Weight.quantize(seeded_weight(K, N, seed=21).cuda(), asym=asym)
+    a = seeded_acts(M, K, seed=22).cuda()
+    got = sk.w4gemm(a, ww, variant=2)
+    assert sk._C.device_status() == 0
+    rows = np.arange(M) if M * N * K <= 2 ** 28 else np.unique(np.concatenate([[0, 127, 128, M - 1], np.random.default_rng(M).choice(M, 48, replace=False)]))
+    want = orc.w4gemm(np.ascontiguousarray(t2n(a)[rows]), t2n(ww.packed), t2n(ww.scales), t2n(ww.zeros))
+    assert_bf16_close(got[torch.from_numpy(rows).cuda()], want, f"w4gemm many tokens M={M} K={K} N={N}")
+
+
+def test_w4gemm_many_tokens_weight_bits_are_the_oracle(sk, orc):
+    """The dequantized weights of the many-token route, read back through one-hot activations, bit for bit."""
+    K, N = 512, 128
+    ww = sk.W4Weight.quantize(seeded_weight(K, N, seed=23).cuda(), asym=True)
+    deq = orc.w4_dequantize(t2n(ww.packed), t2n(ww.scales), t2n(ww.zeros))
+    K, N = 640, 4096                                          # 5 x 32 tiles: enough for the dense route
+    ww = sk.W4Weight.quantize(seeded_weight(K, N, seed=23).cuda(), asym=True)
+    deq = orc.w4_dequantize(t2n(ww.packed), t2n(ww.scales), t2n(ww.zeros))
+    a = torch.eye(K, dtype=torch.bfloat16, device="cuda")   # 640 tokens
+    assert np.array_equal(t2n(sk.w4gemm(a, ww, variant=2)), deq)
