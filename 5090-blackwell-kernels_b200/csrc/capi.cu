@@ -92,7 +92,7 @@ extern "C" int spk_device_status(void* stream, int* code) {
 // ---- a wait that runs out, for tests -------------------------------------------------------------
 namespace spk {
 namespace {
-// One thread waits (a few thousand polls, microseconds) for a barrier phase that nothing completes,
+// One thread waits (a tenth of a millisecond) for a barrier phase that nothing completes,
 // exactly as a broken pipeline would make a kernel of this library wait, records SPK_TIMEOUT in the
 // status word and returns. Before that it leaves `dirty` floats and counters non-zero, which is the
 // state an interrupted split-K kernel leaves behind.
@@ -106,7 +106,8 @@ __global__ void expire_wait_kernel(float* partials, unsigned* counters, int dirt
         ptx::mbar_init(&bar, 1);
         ptx::fence_mbar_init();
         bool done = false;
-        for (int i = 0; i < 4096 && !done; ++i) done = ptx::mbar_try_wait(&bar, 0);
+        const long long t0 = clock64();
+        while (!done && clock64() - t0 < 200000) done = ptx::mbar_try_wait(&bar, 0);  // ~0.1 ms, then give up
         if (!done) atomicCAS(status, 0, SPK_TIMEOUT);
     }
 }

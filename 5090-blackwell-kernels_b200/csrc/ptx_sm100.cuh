@@ -1,9 +1,9 @@
 // Inline-PTX wrappers for sm_100a: mbarrier, bulk asynchronous copies (the TMA engine's
 // untiled form), legacy warp-level mma, and the bounded waits every spin in this library uses.
 //
-// Rule of this library: no unbounded spin on the device. mbar_wait() polls a limited number of
-// times; when the limit is hit it records SPK_TIMEOUT in the device status word and returns
-// false, and the caller drains what it has in flight (again bounded) and returns.
+// Rule of this library: no unbounded spin on the device. mbar_wait() polls for a limited time;
+// when the limit is hit it records SPK_TIMEOUT in the device status word and returns false, and
+// the caller drains what it has in flight (again bounded) and returns.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -40,30 +40,39 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One try: the thread is suspended until the phase completes or a time slice has passed (the hint, in
+// nanoseconds, asks for a long slice: a waiting warp should cost no issue slots, the SM's schedulers are
+// shared with warps that have work). True if the phase has completed.
+constexpr unsigned kSuspendHintNs = 1000000u;
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
     unsigned ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
 
-// Poll limit of one wait. try_wait itself blocks for a hardware-defined slice before it
-// reports failure, so this is on the order of a second of wall time, far beyond any healthy
-// copy or MMA, and short enough that a broken pipeline returns instead of hanging the GPU.
-constexpr unsigned kWaitPolls = 1u << 22;
+// Limit of one wait, in SM clock cycles: about a second at 2 GHz, far beyond any healthy copy or MMA
+// (and beyond a chained launch's wait for the kernel in front), and short enough that a broken
+// pipeline returns instead of hanging the GPU. The limit is a time, not a number of tries, because
+// how long one try stays suspended is up to the hardware.
+constexpr long long kWaitCycles = 2000000000ll;
 
 // Bounded wait for phase `parity` of `bar`. On timeout writes SPK_TIMEOUT (3) to *status
 // (first writer wins) and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* status) {
-    for (unsigned i = 0; i < kWaitPolls; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    do {
         if (mbar_try_wait(bar, parity)) return true;
+    } while (clock64() - t0 < kWaitCycles);
     if (status != nullptr) atomicCAS(status, 0, 3);
     return false;
 }

@@ -101,7 +101,35 @@ struct W4TmemParams {
     float* partials;
     unsigned* counters;
     int* status;
+    int swiglu;  // 1: the strips alternate gate / up columns and C is [M][N / 2] = silu(gate) * up
 };
+
+// The final sums of this lane's column n (TMEM lane = column) for tokens 0 .. NT - 1 -> C. Plain form: one bf16 per
+// token. SwiGLU form (the weight was built with its 16-column strips alternating gate, up, gate, up, ...): lanes
+// 0-15 of a warp hold 16 gate columns and lanes 16-31 the matching up columns, so one shuffle pairs them, and
+// lanes 0-15 store silu(gate) * up, computed in fp32 from the unrounded sums, to column
+// 64 * super-strip + 16 * quarter + lane of the half-width output.
+template <int NT>
+__device__ __forceinline__ void store_outputs(const W4TmemParams& p, const float (&v)[NT], int ss, int quarter, int lane) {
+    if (!p.swiglu) {
+        const int n = ss * 128 + quarter * 32 + lane;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+            if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(v[t]);
+        return;
+    }
+    const int half_n = p.N / 2, col = ss * 64 + quarter * 16 + (lane & 15);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const float up = __shfl_down_sync(0xffffffffu, v[t], 16);
+        if (lane < 16 && t < p.M) {
+            const float gate = v[t];
+            // hardware exp2 / reciprocal: a few ulp of fp32, far below the bf16 rounding of the result, and a
+            // quarter of the instructions of expf and a division (this warp's tail is on the critical path)
+            p.C[static_cast<size_t>(t) * half_n + col] = __float2bfloat16_rn(__fdividef(gate, 1.0f + __expf(-gate)) * up);
+        }
+    }
+}
 
 template <int NT, bool ASYM>
 struct W4TmemSmem {
@@ -476,9 +504,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             const int n = ss * 128 + quarter * 32 + lane;  // TMEM lane = column of the super-strip
             const int seg_chunks = ch - seg_ch0 + 1;
             if (seg_chunks == chunks) {
+                float sums[NT];
 #pragma unroll
-                for (int t = 0; t < NT; ++t)
-                    if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[t]));
+                for (int t = 0; t < NT; ++t) sums[t] = __uint_as_float(v[t]);
+                store_outputs<NT>(p, sums, ss, quarter, lane);
             } else {
                 // The scratch of this kernel is [32-column block][NT / 4][lane][4 tokens]: a lane's partial sums go
                 // out as NT / 4 vector reductions and a warp's reduction covers 512 contiguous bytes (a scalar
@@ -506,13 +535,10 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
 #pragma unroll
                     for (int j = 0; j < NT / 4; ++j)
                         if (4 * j < p.M) __stcg(mine + j * 32, make_float4(0.f, 0.f, 0.f, 0.f));
+                    float sums[NT];
 #pragma unroll
-                    for (int j = 0; j < NT / 4; ++j) {
-                        const float e[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            if (4 * j + q < p.M) p.C[static_cast<size_t>(4 * j + q) * p.N + n] = __float2bfloat16_rn(e[q]);
-                    }
+                    for (int j = 0; j < NT / 4; ++j) sums[4 * j] = w[j].x, sums[4 * j + 1] = w[j].y, sums[4 * j + 2] = w[j].z, sums[4 * j + 3] = w[j].w;
+                    store_outputs<NT>(p, sums, ss, quarter, lane);
                     if (lane == 0) *counter = 0u;
                 }
             }
@@ -576,19 +602,33 @@ int launch_w4_tmem(const void* A, W4TmemParams p, DeviceState* dev, cudaStream_t
 // whether it ran. Measured on B200, 28672 x 4096 weights, graph-timed, including the re-ordering
 // launch: 16 tokens 32.7 us (stream kernel 37.0), 32 tokens 36.1 (shared-memory-operand kernel 45.7),
 // 64 tokens 46.5 (53.0). SPK_W4_TMEM=0 turns the route off, SPK_W4_TMEM_MIN_M moves the lower bound.
+int w4gemm_tmem_run(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N, int K,
+                    cudaStream_t stream, bool* taken, int min_m, bool swiglu);
+
 int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
                     int K, cudaStream_t stream, bool* taken) {
+    static const int min_m = [] {
+        const char* e = std::getenv("SPK_W4_TMEM_MIN_M");
+        return e && *e ? std::atoi(e) : 16;
+    }();
+    return w4gemm_tmem_run(A, packed, scales, zeros, C, M, N, K, stream, taken, min_m, false);
+}
+
+// The fused gate|up + SwiGLU form: N counts the interleaved gate and up columns (C is [M][N / 2]); every token count.
+int w4gemm_tmem_swiglu(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N,
+                       int K, cudaStream_t stream, bool* taken) {
+    return w4gemm_tmem_run(A, packed, scales, zeros, C, M, N, K, stream, taken, 1, true);
+}
+
+int w4gemm_tmem_run(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros, void* C, int M, int N, int K,
+                    cudaStream_t stream, bool* taken, int min_m, bool swiglu) {
     *taken = false;
     static const int enabled = [] {
         const char* e = std::getenv("SPK_W4_TMEM");
         return e && *e ? std::atoi(e) : 1;
     }();
-    static const int min_m = [] {
-        const char* e = std::getenv("SPK_W4_TMEM_MIN_M");
-        return e && *e ? std::atoi(e) : 16;
-    }();
-    if (!enabled || M < min_m || N % 128 != 0 || (K / w4::kGroup) % kChunkGroups != 0) return SPK_OK;
-    if (M == 16 && min_m == 16 && static_cast<int64_t>(K) * N < (int64_t{1} << 25)) return SPK_OK;
+    if ((!enabled && !swiglu) || M < min_m || N % 128 != 0 || (K / w4::kGroup) % kChunkGroups != 0) return SPK_OK;
+    if (!swiglu && M == 16 && min_m == 16 && static_cast<int64_t>(K) * N < (int64_t{1} << 25)) return SPK_OK;
     if (static_cast<int64_t>(64) * N > kPartialFloats || (N / 128) * 4 > kCounters) return SPK_OK;  // scratch is [N][NT]
     if (reinterpret_cast<uintptr_t>(A) % 16 != 0 || static_cast<int64_t>(std::min(M, 64)) * K * 2 > kActScratchBytes) return SPK_OK;
     DeviceState* dev = nullptr;
@@ -602,8 +642,9 @@ int w4gemm_tmem_try(const void* A, const int32_t* packed, const void* scales, co
         p.packed = reinterpret_cast<const unsigned char*>(packed);
         p.scales = static_cast<const unsigned char*>(scales);
         p.zeros = zeros;
-        p.C = static_cast<__nv_bfloat16*>(C) + static_cast<size_t>(m0) * N;
+        p.C = static_cast<__nv_bfloat16*>(C) + static_cast<size_t>(m0) * (swiglu ? N / 2 : N);
         p.M = mc, p.N = N, p.K = K, p.G = K / w4::kGroup;
+        p.swiglu = swiglu ? 1 : 0;
         p.partials = dev->partials, p.counters = dev->counters, p.status = dev->status;
         const void* a = static_cast<const __nv_bfloat16*>(A) + static_cast<size_t>(m0) * K;
         const int nt = mc <= 16 ? 16 : mc <= 32 ? 32 : 64;

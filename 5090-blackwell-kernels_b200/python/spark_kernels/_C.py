@@ -48,6 +48,8 @@ _spk_w4_quantize = _sig("spk_w4_quantize_bf16", [_p, _p, _p, _p, _i, _i, _p])
 _spk_w4_repack = _sig("spk_w4_repack", [_p, _p, _i, _i, _p])
 _spk_w4gemm = _sig("spk_w4gemm_bf16", [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
 _spk_w4gemm_noalloc = _sig("spk_w4gemm_bf16_noalloc", [_p, _p, _p, _p, _p, _i, _i, _i, _p])
+_spk_w4_interleave_gate_up = _sig("spk_w4_interleave_gate_up", [_p, _p, _p, _p, _p, _p, _i, _i, _p])
+_spk_w4gemm_swiglu = _sig("spk_w4gemm_swiglu_bf16", [_p, _p, _p, _p, _p, _i, _i, _i, _p])
 _spk_w4_prefill_reserve = _sig("spk_w4_prefill_reserve", [ctypes.c_longlong])
 _spk_w4gemm_noalloc_status = _sig("spk_w4gemm_noalloc_status", [_p, ctypes.POINTER(_i)])
 _spk_debug_expire_wait = _sig("spk_debug_expire_wait", [_i, _p])
@@ -225,6 +227,48 @@ def w4gemm_noalloc(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
     with torch.cuda.device(a.device):
         _status(_spk_w4gemm_noalloc(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros),
                                     out.data_ptr(), M, N, K, _stream(a)))
+    return out
+
+
+def w4_interleave_gate_up(qweight: torch.Tensor, scales: torch.Tensor, zeros=None):
+    """GPTQ-order tensors of a fused [gate | up] weight -> the same tensors with their 16-column strips
+    alternating gate, up (what `w4gemm_swiglu` expects after `w4_repack`). An addition to the reference's surface."""
+    for t, name in ((qweight, "qweight"), (scales, "scales")):
+        _check_cuda_contig(t, name)
+    _check(qweight.dtype == torch.int32 and qweight.dim() == 2, "qweight must be int32 [K/8, N]")
+    K, N2 = qweight.shape[0] * 8, qweight.shape[1]
+    _check(scales.dtype == torch.bfloat16 and tuple(scales.shape) == (K // W4_GROUP, N2), "scales must be bfloat16 [K/128, N]")
+    if zeros is not None:
+        _check_cuda_contig(zeros, "zeros")
+        _check(zeros.dtype == torch.uint8 and tuple(zeros.shape) == (K // W4_GROUP, N2), "zeros must be uint8 [K/128, N]")
+    with torch.cuda.device(qweight.device):
+        q2, s2 = torch.empty_like(qweight), torch.empty_like(scales)
+        z2 = None if zeros is None else torch.empty_like(zeros)
+        _status(_spk_w4_interleave_gate_up(qweight.data_ptr(), scales.data_ptr(), _ptr(zeros), q2.data_ptr(), s2.data_ptr(),
+                                           _ptr(z2), K, N2, _stream(qweight)))
+    return q2, s2, z2
+
+
+def w4gemm_swiglu(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, zeros=None, out=None) -> torch.Tensor:
+    """bf16 [M, N/2] = silu(a Wgate) * (a Wup) for a gate|up weight whose strips were interleaved with
+    `w4_interleave_gate_up` before `w4_repack`. An addition to the reference's surface."""
+    for t, name in ((a, "a"), (packed, "packed"), (scales, "scales")):
+        _check_cuda_contig(t, name)
+    _check(a.dtype == torch.bfloat16 and a.dim() == 2, "w4gemm_swiglu expects a 2-D bfloat16 a")
+    _check(packed.dtype == torch.int32 and packed.dim() == 2, "packed must be the int32 [N/16, 2K] tensor from w4_repack")
+    M, K = a.shape
+    N2 = packed.shape[0] * 16
+    _check(packed.shape[1] == 2 * K, f"packed is {list(packed.shape)}, expected [N/16, {2 * K}]")
+    _check(scales.dtype == torch.bfloat16 and tuple(scales.shape) == (K // W4_GROUP, N2), f"scales must be bfloat16 [{K // W4_GROUP}, {N2}]")
+    if zeros is not None:
+        _check_cuda_contig(zeros, "zeros")
+        _check(zeros.dtype == torch.uint8 and tuple(zeros.shape) == (K // W4_GROUP, N2), "zeros must be uint8 [K/128, N]")
+    with torch.cuda.device(a.device):
+        if out is None:
+            out = torch.empty((M, N2 // 2), dtype=torch.bfloat16, device=a.device)
+        else:
+            _check(out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N2 // 2) and out.is_contiguous(), "out must be contiguous bfloat16 [M, N/2]")
+        _status(_spk_w4gemm_swiglu(a.data_ptr(), packed.data_ptr(), scales.data_ptr(), _ptr(zeros), out.data_ptr(), M, N2, K, _stream(a)))
     return out
 
 

@@ -66,6 +66,27 @@ def w4gemm(a: torch.Tensor, w, scales: torch.Tensor | None = None, zeros: torch.
     return _C.w4gemm(a, w, scales, zeros, variant, out)
 
 
+class W4GateUpWeight(W4Weight):
+    """The fused [gate | up] weight of an MLP, [K, 2 I], quantized and repacked with its 16-column strips
+    alternating gate, up, so that `w4gemm_swiglu` can apply SwiGLU in the GEMM's epilogue. Not usable with
+    plain `w4gemm` (the column order differs). An addition to the reference's surface."""
+
+    @staticmethod
+    def quantize(w_gate_up: torch.Tensor, asym: bool = False) -> "W4GateUpWeight":
+        qweight, scales, zeros = w4_quantize(w_gate_up, asym)
+        q2, s2, z2 = _C.w4_interleave_gate_up(qweight, scales, zeros)
+        return W4GateUpWeight(w4_repack(q2), s2, z2)
+
+
+def w4gemm_swiglu(a: torch.Tensor, w: W4GateUpWeight, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [M, K] bf16 @ fused int4 gate|up weight [K, 2 I] -> silu(gate) * up, [M, I] bf16, in one GEMM launch
+    per 64 tokens: the activation runs in the GEMM's epilogue on the fp32 sums (the reference runs `w4gemm`
+    and then `swiglu` on its bf16 output, python/spark_kernels/engine.py:447-451). I % 64 == 0, K % 256 == 0."""
+    if not isinstance(w, W4GateUpWeight):
+        raise ValueError("w4gemm_swiglu needs a W4GateUpWeight (strips interleaved gate, up)")
+    return _C.w4gemm_swiglu(a, w.packed, w.scales, w.zeros, out)
+
+
 def num_variants(name: str) -> int:
     return _C.num_variants(name)
 

@@ -47,7 +47,7 @@ SPK_API int spk_init(void);
  * again. Does not cover spk_w4gemm_bf16_noalloc, which has its own status call below. */
 SPK_API int spk_device_status(void* stream, int* code);
 /* Test hook, no counterpart in the reference: launches a one-block kernel that leaves `dirty` words of
- * the split-K scratch non-zero, waits a few thousand polls for a barrier phase nothing completes and
+ * the split-K scratch non-zero, waits a tenth of a millisecond for a barrier phase nothing completes and
  * records SPK_TIMEOUT, i.e. the state a broken pipeline would leave. No fault, no trap; the context
  * stays usable. */
 SPK_API int spk_debug_expire_wait(int dirty, void* stream);
@@ -85,6 +85,17 @@ SPK_API int spk_w4gemm_bf16_noalloc(const void* A, const int32_t* packed, const 
  * clears it, without allocating. A GEMM call does not clear the word, so a timeout stays visible
  * until it is read here. */
 SPK_API int spk_w4gemm_noalloc_status(void* stream, int* code);
+/* No counterpart in the reference, which runs the gate|up GEMM and then a separate swiglu kernel
+ * (python/spark_kernels/engine.py:447-451); its docs name this fusion as the next step (docs/design/llm_quant.md:51-68).
+ * spk_w4_interleave_gate_up re-orders the columns of the GPTQ-order tensors of a fused [gate | up] weight
+ * (N2 = 2 I columns, N2 % 128 == 0) so that 16-column strips alternate gate, up; repack the result with
+ * spk_w4_repack as usual. spk_w4gemm_swiglu_bf16 then computes H bf16 [M][N2 / 2] = silu(A Wgate) * (A Wup)
+ * in one launch per 64 tokens (K % 256 == 0), the activation in fp32 on the unrounded sums. */
+SPK_API int spk_w4_interleave_gate_up(const int32_t* qweight, const void* scales, const uint8_t* zeros,
+                                      int32_t* qweight_out, void* scales_out, uint8_t* zeros_out, int K, int N2,
+                                      void* stream);
+SPK_API int spk_w4gemm_swiglu_bf16(const void* A, const int32_t* packed, const void* scales, const uint8_t* zeros,
+                                   void* H, int M, int N2, int K, void* stream);
 /* No counterpart in the reference (its workspaces grow inside the launchers). From 256 tokens up variant 2
  * dequantizes the weight once into a per-device bf16 scratch of N * K * 2 bytes and runs a dense GEMM; the
  * scratch grows on demand with cudaMalloc. Call this with the largest N * K * 2 you will use before
