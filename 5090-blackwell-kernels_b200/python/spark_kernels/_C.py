@@ -327,6 +327,9 @@ _sig("spk_fp8gemm_v3_route", [])
 _sig("spk_fp8gemm_v3_num_tiles", [])
 _sig("spk_fp8gemm_v3_route_name", [_i, _i, _i, _i], ctypes.c_char_p)
 _sig("spk_fp8gemm_v4_route_name", [_i, _i, _i], ctypes.c_char_p)
+_spk_grouped_gemm_fp8 = _sig("spk_grouped_gemm_fp8", [_p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p])
+_spk_grouped_gemm_swiglu_fp8 = _sig("spk_grouped_gemm_swiglu_fp8", [_p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p])
+_sig("spk_grouped_gemm_supports", [_i, _i, _i])
 _spk_fp4_scale_bytes = _sig("spk_fp4_scale_bytes", [_i, _i, _i], ctypes.c_size_t)
 _spk_fp4_quantize = _sig("spk_fp4_quantize", [_p, _p, _p, _i, _i, _p, _i, _p, _p, _p])
 _spk_fp4gemm = _sig("spk_fp4gemm", [_p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p])
@@ -385,6 +388,29 @@ def fp8gemm(a, b_t, scale_a=None, scale_b=None, variant: int = -1, sfa=None, sfb
         else:
             _status(_spk_fp8gemm(a.data_ptr(), b_t.data_ptr(), c.data_ptr(), M, N, K, sa, sb, v, _stream(a)))
     return c
+
+
+def grouped_gemm_fp8(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, scale_a=None, scale_b=None, swiglu: bool = False):
+    """Every expert's fp8 GEMM in one launch (reference python/csrc/bindings.cpp grouped_gemm_fp8 /
+    grouped_gemm_swiglu_fp8): a e4m3 [T, K] with rows sorted by expert, w e4m3 [E, N, K], offsets int32 [E + 1] on the
+    device, scale_a f32 [1] and scale_b f32 [E] (or None) -> bf16 [T, N], or [T, N / 2] = silu(gate) * up with `swiglu`
+    (w rows alternating gate_j, up_j)."""
+    for t, name in ((a, "a"), (w, "w"), (offsets, "offsets")):
+        _check_cuda_contig(t, name)
+    _check(a.dtype == _FP8 and w.dtype == _FP8 and a.dim() == 2 and w.dim() == 3, "grouped_gemm_fp8 expects float8_e4m3fn a [T, K] and w [E, N, K]")
+    T, K = a.shape
+    E, N, K2 = w.shape
+    _check(K2 == K, "inner dimensions mismatch")
+    _check(offsets.dtype == torch.int32 and tuple(offsets.shape) == (E + 1,), "offsets must be int32 [E + 1]")
+    for sc, n, name in ((scale_a, 1, "scale_a"), (scale_b, E, "scale_b")):
+        if sc is not None:
+            _check_cuda_contig(sc, name)
+            _check(sc.dtype == torch.float32 and sc.numel() == n, f"{name} must be float32 with {n} element(s)")
+    with torch.cuda.device(a.device):
+        out = torch.empty((T, N // 2 if swiglu else N), dtype=torch.bfloat16, device=a.device)
+        fn = _spk_grouped_gemm_swiglu_fp8 if swiglu else _spk_grouped_gemm_fp8
+        _status(fn(a.data_ptr(), w.data_ptr(), offsets.data_ptr(), out.data_ptr(), T, E, N, K, _ptr(scale_a), _ptr(scale_b), _stream(a)))
+    return out
 
 
 def fp8gemm_v3_set_route(route: int) -> int:

@@ -120,6 +120,18 @@ def fp4gemm(a, b_t, sfa, sfb, scale_a=None, scale_b=None, fmt: str = "nvfp4", va
     return _C.fp4gemm(a, b_t, sfa, sfb, scale_a, scale_b, fmt, variant)
 
 
+def grouped_gemm_fp8(a, w, offsets, scale_a=None, scale_b=None):
+    """Grouped fp8 GEMM over the experts of a mixture-of-experts layer, one launch, no host sync: row r of a [T, K]
+    (sorted by expert, expert e owning rows offsets[e] .. offsets[e + 1] - 1) times w[e]^T, w [E, N, K] -> bf16 [T, N]
+    scaled by scale_a [1] * scale_b[e]. N % 128 == 0, K % 128 == 0, E <= 512."""
+    return _C.grouped_gemm_fp8(a, w, offsets, scale_a, scale_b, False)
+
+
+def grouped_gemm_swiglu_fp8(a, w, offsets, scale_a=None, scale_b=None):
+    """The same with the SwiGLU of an expert's MLP in the epilogue: w rows alternate gate_j, up_j; -> bf16 [T, N / 2]."""
+    return _C.grouped_gemm_fp8(a, w, offsets, scale_a, scale_b, True)
+
+
 def fp8_quantize_block128(x, block_rows: int):
     return _C.fp8_quantize_block128(x, block_rows)
 

@@ -148,6 +148,18 @@ SPK_API int spk_fp8gemm_block128(const void* A, const void* Bt, void* C, int M, 
 SPK_API int spk_fp8_quantize_block128(const float* x, unsigned char* q, float* scales, int rows, int K,
                                       int block_rows, void* stream);
 
+/* reference include/spark/kernels.h:476-494 (grouped_gemm_fp8, grouped_gemm_swiglu_fp8, grouped_gemm_supports): every
+ * expert's GEMM of a mixture-of-experts layer in one persistent launch. A e4m3 [T][K], rows sorted by expert;
+ * offsets int32 [E + 1] on the device (offsets[0] == 0, offsets[E] == T, empty experts allowed); W e4m3 [E][N][K];
+ * C bf16 [T][N] = scale_a * scale_b[e] * A W[e]^T (scale_a device fp32 [1], scale_b device fp32 [E], either may be
+ * NULL: 1). The SwiGLU form takes W with rows alternating gate_j, up_j and writes C [T][N / 2] = silu(G) * U in
+ * fp32 from the two scaled sums. 1 <= E <= 512, N % 128 == 0, K % 128 == 0, 16-byte aligned A, W, C. */
+SPK_API int spk_grouped_gemm_supports(int E, int N, int K);
+SPK_API int spk_grouped_gemm_fp8(const void* A, const void* W, const int32_t* offsets, void* C, int T, int E, int N, int K,
+                                 const float* scale_a, const float* scale_b, void* stream);
+SPK_API int spk_grouped_gemm_swiglu_fp8(const void* A, const void* W, const int32_t* offsets, void* C, int T, int E, int N,
+                                        int K, const float* scale_a, const float* scale_b, void* stream);
+
 /* ---- fp4 e2m1 (NVFP4, MXFP4) -------------------------------------------------------------- */
 
 enum { SPK_FP4_NVFP4 = 0, SPK_FP4_MXFP4 = 1 };  /* reference kernels.h:322 */
