@@ -22,17 +22,20 @@
 //
 // The two launches are chained programmatically (spk_common.cuh): the GEMM's CTAs become resident,
 // set up and start streaming weights while the re-ordering kernel (and, SM by SM, the tail of the
-// GEMM before it) is still running; only the activation producer and the epilogue warps wait for it.
+// GEMM before it) is still running; only the activation producer, the MMA and the epilogue warps wait for it.
 //
 // One persistent CTA per SM owns a contiguous range of (128-column super-strip, 2-group chunk)
-// units. Roles (22 warps):
+// units. Roles (23 warps):
 //   warps 0-15  dequant: strip 2 (w % 4) + (w / 4) % 2 (its 16 TMEM lanes lie in the lane quarter
-//               w % 4 that the warp may access), chunks of parity w / 8 of the CTA's sequence
-//   warps 16-19 epilogue (TMEM lane quarter w % 4)
-//   warp 20     MMA: loop warp-wide, one elected lane issues 16 tcgen05.mma per chunk
-//   warp 21     activation producer (one elected lane, two TMA loads per group)
-// TMEM columns: accumulators at 0 and NT (double buffered), weights at 128 + 128 cs + 64 sub +
-// 32 h + 8 r for chunk stage cs (3), group sub, unit h, MMA step r.
+//               w % 4 that the warp may access), chunks of parity w / 8 (the warp's set) of the CTA's sequence
+//   warps 16-19 epilogue (TMEM lane quarter w % 4): adds the two sets' accumulators of a K segment
+//   warps 20-21 MMA, one per set: loop warp-wide, one elected lane issues the 16 tcgen05.mma of a chunk
+//               of its set into the set's accumulator
+//   warp 22     activation producer (one elected lane, four TMA loads per chunk)
+// TMEM columns: accumulator (set s, buffer b) at (s * bufs + b) * NT (two buffers per set up to 32
+// tokens, one at 64), weights at 128 + 128 cs + 64 sub + 32 h + 8 r for chunk stage cs (3), group sub,
+// unit h, MMA step r. The activations of a chunk live in shared-memory stage cs as well, so one commit
+// of the chunk's MMAs frees both.
 #include <algorithm>
 
 #include "spk_common.cuh"
@@ -53,28 +56,25 @@ constexpr int kChunkGroups = 2;   // groups per chunk
 constexpr int kSets = 2;          // dequant warps per strip; set s takes chunks of parity s
 constexpr int DW = kStrips * kSets;
 constexpr int kChunkStages = 3;   // chunks of dequantized weights resident in TMEM
-// Ring depths. The activation tiles come from L2 through the same TMA queue as the weight stream, so a
-// tile requested when its slot frees arrives only after the weight copies queued in front of it
-// (measured ~1.9 us from request to use with 96 KiB of weight copies in flight per SM): the slots of
-// the activation ring divided by that round trip is a hard ceiling on groups per second, whatever the
-// dequant warps can do (4 slots held every token count to one chunk per ~1850 cycles). Hence a shallow
-// code ring (2 slots of 2 KiB per warp: 64 KiB per SM in flight, enough for the HBM rate) and as many
-// activation slots as shared memory allows (8 at 64 tokens, 16 below).
+constexpr int kStageBars = kSets * kChunkStages;  // barrier sets of the chunk stages (see the kernel)
+// Per-warp ring of one-chunk code pieces (2 KiB each): 2 slots per warp are 64 KiB per SM in flight, enough for the
+// HBM rate; deeper rings were measured and change nothing (the kernel is not bound by the stream).
 #ifndef SPK_TMEM_CODE_SLOTS
 #define SPK_TMEM_CODE_SLOTS 2
 #endif
-#ifndef SPK_TMEM_ACT_BYTES
-#define SPK_TMEM_ACT_BYTES (128 * 1024)
-#endif
-constexpr int kCodeSlots = SPK_TMEM_CODE_SLOTS;  // per-warp ring of one-chunk code pieces
-template <int NT>
-constexpr int act_stages() {  // one group per slot
-    return SPK_TMEM_ACT_BYTES / (2 * NT * 128) > 16 ? 16 : SPK_TMEM_ACT_BYTES / (2 * NT * 128);
-}
-constexpr int kEpilogueWarp0 = DW, kMmaWarp = DW + 4, kProducerWarp0 = DW + 5;
-constexpr int kThreadsT = (DW + 6) * 32;
+constexpr int kCodeSlots = SPK_TMEM_CODE_SLOTS;
+// One MMA warp per dequant set. The MMA issuer is a serial instruction stream in which every barrier wait, fence and
+// commit costs 100-300 cycles (device-clock traces: ~2000 cycles per chunk with one issuer, which was the whole kernel's
+// pace: removing the dequant arithmetic, the activation loads or the weight stream changed nothing). Two issuers on two
+// schedulers, each with its own accumulator (summed by the epilogue), halve that, and the activations of a chunk share
+// the chunk's stage barriers (one wait and one commit per chunk instead of three each).
+constexpr int kEpilogueWarp0 = DW, kMmaWarp0 = DW + 4, kProducerWarp0 = DW + 4 + kSets;
+constexpr int kThreadsT = (DW + 5 + kSets) * 32;
 constexpr int kTmemColsT = 512;
 constexpr int kWeightCol0 = 128;  // first TMEM column of the weight stages
+// accumulators per set: double buffered where the 128 columns in front of the weights allow
+template <int NT>
+constexpr int acc_bufs() { return 2 * kSets * NT <= kWeightCol0 ? 2 : 1; }
 
 // Development aid, compiled in only with -DSPK_W4_TRACE: device clock stamps of the roles of a few CTAs,
 // written to a buffer set with spk_debug_w4_trace (layout [cta slot][warp][kTraceEvents]).
@@ -104,30 +104,34 @@ struct W4TmemParams {
     int swiglu;  // 1: the strips alternate gate / up columns and C is [M][N / 2] = silu(gate) * up
 };
 
-// The final sums of this lane's column n (TMEM lane = column) for tokens 0 .. NT - 1 -> C. Plain form: one bf16 per
+// The final sums of this lane's column n (TMEM lane = column) for tokens t0 .. t0 + TB - 1 -> C. Plain form: one bf16 per
 // token. SwiGLU form (the weight was built with its 16-column strips alternating gate, up, gate, up, ...): lanes
 // 0-15 of a warp hold 16 gate columns and lanes 16-31 the matching up columns, so one shuffle pairs them, and
 // lanes 0-15 store silu(gate) * up, computed in fp32 from the unrounded sums, to column
 // 64 * super-strip + 16 * quarter + lane of the half-width output.
-template <int NT>
-__device__ __forceinline__ void store_outputs(const W4TmemParams& p, const float (&v)[NT], int ss, int quarter, int lane) {
+template <int TB>
+__device__ __forceinline__ void store_outputs(const W4TmemParams& p, const float (&v)[TB], int t0, int ss, int quarter, int lane) {
     if (!p.swiglu) {
         const int n = ss * 128 + quarter * 32 + lane;
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
-            if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __float2bfloat16_rn(v[t]);
+        for (int t = 0; t < TB; ++t)
+            if (t0 + t < p.M) p.C[static_cast<size_t>(t0 + t) * p.N + n] = __float2bfloat16_rn(v[t]);
         return;
     }
     const int half_n = p.N / 2, col = ss * 64 + quarter * 16 + (lane & 15);
+    // Every lane computes (the upper half's results are unused): with the arithmetic under the `lane < 16` branch the
+    // shuffle -> exp -> reciprocal chains ran one after another, ~100 cycles each, on this warp's tail.
+    // Hardware exp2 / reciprocal: a few ulp of fp32, far below the bf16 rounding of the result.
+    __nv_bfloat16 h[TB];
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-        const float up = __shfl_down_sync(0xffffffffu, v[t], 16);
-        if (lane < 16 && t < p.M) {
-            const float gate = v[t];
-            // hardware exp2 / reciprocal: a few ulp of fp32, far below the bf16 rounding of the result, and a
-            // quarter of the instructions of expf and a division (this warp's tail is on the critical path)
-            p.C[static_cast<size_t>(t) * half_n + col] = __float2bfloat16_rn(__fdividef(gate, 1.0f + __expf(-gate)) * up);
-        }
+    for (int t = 0; t < TB; ++t) {
+        const float up = __shfl_down_sync(0xffffffffu, v[t], 16), gate = v[t];
+        h[t] = __float2bfloat16_rn(__fdividef(gate, 1.0f + __expf(-gate)) * up);
+    }
+    if (lane < 16) {
+#pragma unroll
+        for (int t = 0; t < TB; ++t)
+            if (t0 + t < p.M) p.C[static_cast<size_t>(t0 + t) * half_n + col] = h[t];
     }
 }
 
@@ -139,8 +143,8 @@ struct W4TmemSmem {
     static constexpr int kCodeRing = DW * kCodeSlots * kSlotBytes;
     static constexpr int kCodeArrivals = 1 + 2 * kChunkGroups + (ASYM ? kChunkGroups : 0);
     static constexpr int kBarriers = 1024;
-    static constexpr int kActStages = act_stages<NT>();
-    static constexpr int kTotal = 1024 + kActStages * kActBytes + kCodeRing + kBarriers;
+    static constexpr int kActChunkBytes = kChunkGroups * kActBytes;  // a chunk's activations: one stage per TMEM chunk stage
+    static constexpr int kTotal = 1024 + kChunkStages * kActChunkBytes + kCodeRing + kBarriers;
 };
 
 __device__ __forceinline__ void cp_async16_t(void* dst, const void* src) {
@@ -213,21 +217,24 @@ __device__ __forceinline__ void mma_f16_ta_acc(uint32_t tmem_d, uint32_t tmem_a,
 template <int NT, bool ASYM>
 __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_constant__ CUtensorMap map_act, const W4TmemParams p) {
     using L = W4TmemSmem<NT, ASYM>;
-    constexpr int kActStages = L::kActStages;
+    constexpr int kAccBufs = acc_bufs<NT>();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t{1023});
     unsigned char* acts = base;
-    unsigned char* codes = acts + kActStages * L::kActBytes;
+    unsigned char* codes = acts + kChunkStages * L::kActChunkBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(codes + L::kCodeRing);
-    uint64_t* act_full = bars;                    // [AS] TMA
-    uint64_t* act_empty = act_full + kActStages;  // [AS] MMA commit
-    uint64_t* a_ready = act_empty + kActStages;   // [CS] the 8 dequant warps of the chunk's set
-    uint64_t* a_free = a_ready + kChunkStages;    // [CS] MMA commit
-    uint64_t* acc_ready = a_free + kChunkStages;  // [2] MMA commit
-    uint64_t* acc_free = acc_ready + 2;           // [2] 4 epilogue warps
-    uint64_t* code_bar = acc_free + 2;            // [DW][kCodeSlots]
-    uint64_t* drain_bar = code_bar + DW * kCodeSlots;  // MMA commit on the error path only
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+    // The barriers of the chunk visited i-th are those of index i % kStageBars (its stage is i % kChunkStages): with one
+    // barrier per stage the two sets would each see only every other phase of it, and a parity test cannot tell
+    // "phase k complete" from "phase k - 1 not yet complete" (a set that ran one chunk ahead of the other took stale
+    // weights that way). Indexed by i % 6 every waiter sees consecutive phases of the barriers it waits on.
+    uint64_t* act_full = bars;                            // [SB] TMA: the chunk's activations have landed
+    uint64_t* a_ready = act_full + kStageBars;            // [SB] the 8 dequant warps of the chunk's set
+    uint64_t* a_free = a_ready + kStageBars;              // [SB] MMA commit: TMEM stage and activation stage may be refilled
+    uint64_t* acc_ready = a_free + kStageBars;            // [sets][bufs] MMA commit
+    uint64_t* acc_free = acc_ready + kSets * kAccBufs;    // [sets][bufs] 4 epilogue warps
+    uint64_t* code_bar = acc_free + kSets * kAccBufs;     // [DW][kCodeSlots]
+    uint64_t* drain_bar = code_bar + DW * kCodeSlots;     // [sets] MMA commit on the error path only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + kSets);
 
     pdl_release();  // a chained kernel behind this one may become resident as this grid's CTAs exit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -249,23 +256,20 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             ptx::fence_mbar_init();
         }
     } else if (warp == kEpilogueWarp0) {
-        if (lane < kActStages) {
+        if (lane < kStageBars) {
             mbar_init(&act_full[lane], 1);
-            mbar_init(&act_empty[lane], 1);
-        }
-        if (lane < kChunkStages) {
             mbar_init(&a_ready[lane], kStrips);
             mbar_init(&a_free[lane], 1);
         }
-        if (lane < 2) {
+        if (lane < kSets * kAccBufs) {
             mbar_init(&acc_ready[lane], 1);
             mbar_init(&acc_free[lane], 4);
         }
-        if (lane == 2) mbar_init(drain_bar, 1);
+        if (lane < kSets) mbar_init(&drain_bar[lane], 1);
         ptx::fence_mbar_init();
         if (lane == 0) umma::prefetch_tensormap(&map_act);
     }
-    if (warp == kMmaWarp) umma::tmem_alloc(tmem_slot, kTmemColsT);
+    if (warp == kMmaWarp0) umma::tmem_alloc(tmem_slot, kTmemColsT);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -307,8 +311,8 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         for (int i = 0; i < kCodeSlots; ++i) issue();
 
         const int n_mine = n_chunks > set ? (n_chunks - set + 1) / 2 : 0;
-        int slot_i = 0, cs = set;  // chunk stage of the chunks visited set-th, (set + 2)-th, ...
-        unsigned code_ph = 0, ph = 0;
+        int slot_i = 0, cs = set, bi = set;  // chunk stage and barrier index of the chunks visited set-th, (set + 2)-th, ...
+        unsigned code_ph = 0, bph = 0;
         bool ok = true, chained = false;
         int it = 0;
         for (; it < n_mine && ok; ++it) {
@@ -347,7 +351,9 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                         chained = true;
                     }
                     W4_TRACE();  // + 2: first group dequantized
-                    ok = __all_sync(0xffffffffu, mbar_wait(&a_free[cs], ph ^ 1u, p.status));
+                    // chunk j waits for the MMAs of chunk j - 3: barrier (j - 3) % 6, its phase (j - 3) / 6
+                    ok = __all_sync(0xffffffffu, mbar_wait(&a_free[bi >= kChunkStages ? bi - kChunkStages : bi + kChunkStages],
+                                                           bi >= kChunkStages ? bph : bph ^ 1u, p.status));
                     if (!ok) break;
                     umma::fence_after_sync();
                     W4_TRACE();  // + 3: TMEM stage free
@@ -373,9 +379,11 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             tmem_st_wait();
             umma::fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&a_ready[cs]);
+            if (lane == 0) mbar_arrive(&a_ready[bi]);
             cs += kSets;
-            if (cs >= kChunkStages) cs -= kChunkStages, ph ^= 1u;
+            if (cs >= kChunkStages) cs -= kChunkStages;
+            bi += kSets;
+            if (bi >= kStageBars) bi -= kStageBars, bph ^= 1u;
         }
         if (!ok) {
             // A wait gave up: let the code copies still in flight into this warp's ring land (bounded,
@@ -387,137 +395,154 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             }
         }
     } else if (warp == kProducerWarp0) {
-        // ================= activation producer: one 128-k group (two units) per slot =================
+        // ================= activation producer: a chunk's groups go to the chunk's stage =================
         pdl_wait();  // the re-ordered activations are written by the kernel in front of this one
-        int s = 0;
-        unsigned ph = 0;
-        bool ok = true;
-        for (int i = 0; i < n_chunks && ok; ++i) {
+        int cs = 0, bi = 0;
+        unsigned bph = 0;
+        for (int i = 0; i < n_chunks; ++i) {
             const int ch = visit.at(i) % chunks;
-            for (int sub = 0; sub < kChunkGroups && ok; ++sub) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&act_empty[s], ph ^ 1u, p.status));
-                if (!ok) break;
-                if (umma::elect_one()) {
-                    mbar_arrive_expect_tx(&act_full[s], L::kActBytes);
+            // the stage is free once the MMAs of three chunks ago have read it (the first three find it fresh)
+            if (i >= kChunkStages &&
+                !__all_sync(0xffffffffu, mbar_wait(&a_free[bi >= kChunkStages ? bi - kChunkStages : bi + kChunkStages],
+                                                   bi >= kChunkStages ? bph : bph ^ 1u, p.status)))
+                break;
+            if (umma::elect_one()) {
+                mbar_arrive_expect_tx(&act_full[bi], L::kActChunkBytes);
+#pragma unroll
+                for (int sub = 0; sub < kChunkGroups; ++sub) {
                     const int x = (ch * kChunkGroups + sub) * 256;  // byte offset of the group in a token row
-                    umma::tma_load_2d(acts + s * L::kActBytes, &map_act, x, 0, &act_full[s]);
-                    umma::tma_load_2d(acts + s * L::kActBytes + NT * 128, &map_act, x + 128, 0, &act_full[s]);
+                    unsigned char* dst = acts + cs * L::kActChunkBytes + sub * L::kActBytes;
+                    umma::tma_load_2d(dst, &map_act, x, 0, &act_full[bi]);
+                    umma::tma_load_2d(dst + NT * 128, &map_act, x + 128, 0, &act_full[bi]);
                 }
-                __syncwarp();
-                if (++s == kActStages) s = 0, ph ^= 1u;
             }
+            __syncwarp();
+            if (++cs == kChunkStages) cs = 0;
+            if (++bi == kStageBars) bi = 0, bph ^= 1u;
         }
-    } else if (warp == kMmaWarp) {
-        // ================= MMA issuer: the loop runs warp-wide, one elected lane issues =================
-        // This warp shares its scheduler with four dequant warps that always have work, so every
-        // instruction here costs several cycles of the critical path: descriptors are built once and
-        // advanced with 32-bit adds, and only the first MMA of a K segment carries a run-time predicate.
+    } else if (warp >= kMmaWarp0) {
+        // ================= MMA issuers: warp kMmaWarp0 + s takes the chunks of set s into accumulator s =================
+        // The loop runs warp-wide, one elected lane issues. Descriptors are built once and advanced with 32-bit adds;
+        // only the first MMA of this set's part of a K segment carries a run-time predicate.
+        const int set = warp - kMmaWarp0;
         constexpr uint32_t idesc = umma::instr_desc(128, NT, 1, 1);  // bf16 x bf16 -> f32
         const uint64_t bdesc0 = umma::smem_desc_k128(acts);
         const uint32_t bd_lo0 = static_cast<uint32_t>(bdesc0), bd_hi = static_cast<uint32_t>(bdesc0 >> 32);
-        int seg = 0, cs = 0, as = 0;
-        unsigned ph = 0, aph = 0;
+        int segn = 0, cs = set, bi = set;  // K segments this set has contributed to; stage i % 3 and barriers i % 6 of chunk i
+        unsigned bph = 0;
         bool ok = true, fresh = true;
         // Everything this warp waits for needs the activations, which the producer requests only after the
         // kernel in front of a chained launch has completed; its bounded waits start counting from there.
         pdl_wait();
-        for (int i = 0; i < n_chunks && ok; ++i) {
+        for (int i = set; i < n_chunks && ok; i += kSets) {
             const int ch = visit.at(i) % chunks;
-            const int buf = seg & 1;
+            const int buf = segn % kAccBufs;
+            uint64_t* my_ready = &acc_ready[set * kAccBufs + buf];
             if (fresh) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&acc_free[buf], ((seg >> 1) & 1) ^ 1, p.status));
+                ok = __all_sync(0xffffffffu, mbar_wait(&acc_free[set * kAccBufs + buf], ((segn / kAccBufs) & 1) ^ 1, p.status));
                 if (!ok) break;
             }
-            const uint32_t acc = tmem_base + buf * NT;
-            W4_TRACE();  // MMA 2 + 2 chunk: waiting for the chunk's weights
-            ok = __all_sync(0xffffffffu, mbar_wait(&a_ready[cs], ph, p.status));
+            const uint32_t acc = tmem_base + (set * kAccBufs + buf) * NT;
+            W4_TRACE();  // MMA 2 + 2 chunk: waiting for the chunk's weights and activations
+            ok = __all_sync(0xffffffffu, mbar_wait(&a_ready[bi], bph, p.status) && mbar_wait(&act_full[bi], bph, p.status));
             if (!ok) break;
-            W4_TRACE();  // + 1: weights ready
-#pragma unroll
-            for (int sub = 0; sub < kChunkGroups; ++sub) {
-                ok = ok && __all_sync(0xffffffffu, mbar_wait(&act_full[as], aph, p.status));
-                if (ok) {
-                    umma::fence_after_sync();
-                    const uint32_t bd = bd_lo0 + static_cast<uint32_t>(as) * (L::kActBytes >> 4);
-                    const uint32_t wa = tmem_base + kWeightCol0 + cs * 128 + sub * 64;
-                    if (umma::elect_one()) {
-                        if (sub == 0)
-                            mma_f16_ta(acc, wa, make_desc(bd, bd_hi), idesc, !fresh);
-                        else
-                            mma_f16_ta_acc(acc, wa, make_desc(bd, bd_hi), idesc);
-#pragma unroll
-                        for (int hr = 1; hr < 8; ++hr)
-                            mma_f16_ta_acc(acc, wa + (hr >> 2) * 32 + (hr & 3) * 8,
-                                           make_desc(bd + (hr >> 2) * (NT * 128 >> 4) + 2 * (hr & 3), bd_hi), idesc);
-                        umma::mma_commit(&act_empty[as]);
-                    }
-                    __syncwarp();
-                    if (++as == kActStages) as = 0, aph ^= 1u;
-                }
-            }
-            if (!ok) break;
-            fresh = false;
-            const bool seg_end = visit.ends_segment(i, ch, chunks);
+            W4_TRACE();  // + 1: both ready
+            umma::fence_after_sync();
+            // this set's last chunk of the segment: the segment ends here or with the other set's next chunk
+            bool seg_end = visit.ends_segment(i, ch, chunks) || i + kSets >= n_chunks;
+            if (!seg_end) seg_end = visit.ends_segment(i + 1, visit.at(i + 1) % chunks, chunks);
             if (umma::elect_one()) {
-                umma::mma_commit(&a_free[cs]);
-                if (seg_end) umma::mma_commit(&acc_ready[buf]);
+                const uint32_t bd = bd_lo0 + static_cast<uint32_t>(cs) * (L::kActChunkBytes >> 4);
+                const uint32_t wa = tmem_base + kWeightCol0 + cs * 128;
+                mma_f16_ta(acc, wa, make_desc(bd, bd_hi), idesc, !fresh);
+#pragma unroll
+                for (int j = 1; j < 8 * kChunkGroups; ++j) {  // group j / 8, MMA step j % 8 (unit (j / 4) % 2, step j % 4 of it)
+                    const int sub = j >> 3, hr = j & 7;
+                    mma_f16_ta_acc(acc, wa + sub * 64 + (hr >> 2) * 32 + (hr & 3) * 8,
+                                   make_desc(bd + sub * (L::kActBytes >> 4) + (hr >> 2) * (NT * 128 >> 4) + 2 * (hr & 3), bd_hi), idesc);
+                }
+                umma::mma_commit(&a_free[bi]);
+                if (seg_end) umma::mma_commit(my_ready);
             }
             __syncwarp();
-            if (++cs == kChunkStages) cs = 0, ph ^= 1u;
-            if (seg_end) ++seg, fresh = true;
+            cs += kSets;
+            if (cs >= kChunkStages) cs -= kChunkStages;
+            bi += kSets;
+            if (bi >= kStageBars) bi -= kStageBars, bph ^= 1u;
+            fresh = seg_end;
+            if (seg_end) ++segn;
         }
         if (!ok) {
             // MMAs already issued may still be reading TMEM and shared memory: one more commit, and a
             // bounded wait for it, before the CTA frees them.
-            if (umma::elect_one()) umma::mma_commit(drain_bar);
+            if (umma::elect_one()) umma::mma_commit(&drain_bar[set]);
             __syncwarp();
-            (void)mbar_wait(drain_bar, 0, nullptr);
+            (void)mbar_wait(&drain_bar[set], 0, nullptr);
         }
     } else {
         // ================= epilogue warps: TMEM lane quarter = warp % 4 =================
         const int quarter = warp & 3;
         pdl_wait();  // C and the split-K scratch may still be in use by the kernels in front
-        int seg = 0, seg_ch0 = -1;
+        int segn[kSets] = {}, seg_ch0 = -1, i0 = 0;  // segments each set has contributed to; first chunk of the open segment
         bool ok = true;
         for (int i = 0; i < n_chunks && ok; ++i) {
             const int f = visit.at(i), ss = f / chunks, ch = f - ss * chunks;
             if (seg_ch0 < 0) seg_ch0 = ch;
             if (!visit.ends_segment(i, ch, chunks)) continue;
-            const int buf = seg & 1;
+            // The segment is the chunks visited i0 .. i; set s holds the partial sum of those of parity s (if any).
             W4_TRACE();  // epilogue 2 + 3 seg: waiting for a segment
-            ok = __all_sync(0xffffffffu, mbar_wait(&acc_ready[buf], (seg >> 1) & 1, p.status));
-            if (!ok) break;
-            W4_TRACE();  // + 1: accumulator ready
-            umma::fence_after_sync();
-            uint32_t v[NT];
+            int slots[kSets], n_slots = 0;
 #pragma unroll
-            for (int c0 = 0; c0 < NT; c0 += 16) {
-                uint32_t r[16];
-                umma::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * NT + c0, r);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[c0 + j] = r[j];
+            for (int s = 0; s < kSets; ++s) {
+                const int mine = (i + 2 - s) / 2 - (i0 + 1 - s) / 2;  // chunks of parity s among i0 .. i
+                if (mine == 0 || !ok) continue;
+                const int slot = s * kAccBufs + segn[s] % kAccBufs;
+                ok = __all_sync(0xffffffffu, mbar_wait(&acc_ready[slot], (segn[s] / kAccBufs) & 1, p.status));
+                slots[n_slots++] = slot;
+                ++segn[s];
             }
-            umma::tmem_ld_wait();
-            umma::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_free[buf]);
+            if (!ok) break;
+            i0 = i + 1;
+            umma::fence_after_sync();
+            W4_TRACE();  // + 1: accumulators ready
             const int n = ss * 128 + quarter * 32 + lane;  // TMEM lane = column of the super-strip
             const int seg_chunks = ch - seg_ch0 + 1;
-            if (seg_chunks == chunks) {
-                float sums[NT];
+            const bool whole = seg_chunks == chunks;
+            // The scratch of this kernel is [32-column block][NT / 4][lane][4 tokens]: a lane's partial sums go
+            // out as NT / 4 vector reductions and a warp's reduction covers 512 contiguous bytes (a scalar
+            // reduction per token row cost ~100 cycles each here).
+            float4* mine = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane;
+            constexpr int TB = NT < 32 ? NT : 32;  // tokens per pass: the sums of 64 tokens do not fit the registers
 #pragma unroll
-                for (int t = 0; t < NT; ++t) sums[t] = __uint_as_float(v[t]);
-                store_outputs<NT>(p, sums, ss, quarter, lane);
-            } else {
-                // The scratch of this kernel is [32-column block][NT / 4][lane][4 tokens]: a lane's partial sums go
-                // out as NT / 4 vector reductions and a warp's reduction covers 512 contiguous bytes (a scalar
-                // reduction per token row cost ~100 cycles each here).
-                float4* mine = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(n >> 5) * (NT / 4) * 32 + lane;
+            for (int t0 = 0; t0 < NT; t0 += TB) {
+                float v[TB];
 #pragma unroll
-                for (int t = 0; t < NT; t += 4)
-                    if (t < p.M)
-                        red_add_v4(reinterpret_cast<float*>(mine + (t / 4) * 32), __uint_as_float(v[t]), __uint_as_float(v[t + 1]),
-                                   __uint_as_float(v[t + 2]), __uint_as_float(v[t + 3]));
+                for (int k = 0; k < kSets; ++k) {
+                    if (k >= n_slots) continue;
+#pragma unroll
+                    for (int c0 = 0; c0 < TB; c0 += 16) {
+                        uint32_t r[16];
+                        umma::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + slots[k] * NT + t0 + c0, r);
+                        umma::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[c0 + j] = k == 0 ? __uint_as_float(r[j]) : v[c0 + j] + __uint_as_float(r[j]);
+                    }
+                }
+                if (t0 + TB == NT) {  // everything is in registers: the MMA warps may overwrite the accumulators
+                    umma::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0)
+                        for (int k = 0; k < n_slots; ++k) mbar_arrive(&acc_free[slots[k]]);
+                }
+                if (whole) {
+                    store_outputs<TB>(p, v, t0, ss, quarter, lane);
+                } else {
+#pragma unroll
+                    for (int t = 0; t < TB; t += 4)
+                        if (t0 + t < p.M) red_add_v4(reinterpret_cast<float*>(mine + ((t0 + t) / 4) * 32), v[t], v[t + 1], v[t + 2], v[t + 3]);
+                }
+            }
+            if (!whole) {
                 // Completion right away (this warp has nothing else to do until the next segment ends): one fence,
                 // then the per-(super-strip, quarter) counter; whoever brings it to `chunks` owns the sums.
                 __threadfence();
@@ -528,21 +553,23 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                 done = __shfl_sync(0xffffffffu, done, 0);
                 if (done + static_cast<unsigned>(seg_chunks) == static_cast<unsigned>(chunks)) {
                     __threadfence();
-                    // this lane's NT sums: NT / 4 vector loads in one round trip, re-zero, store bf16
-                    float4 w[NT / 4];
+                    // this lane's sums, TB tokens at a time: vector loads in one round trip, re-zero, store bf16
 #pragma unroll
-                    for (int j = 0; j < NT / 4; ++j) w[j] = 4 * j < p.M ? __ldcg(mine + j * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int t0 = 0; t0 < NT; t0 += TB) {
+                        float4 w[TB / 4];
 #pragma unroll
-                    for (int j = 0; j < NT / 4; ++j)
-                        if (4 * j < p.M) __stcg(mine + j * 32, make_float4(0.f, 0.f, 0.f, 0.f));
-                    float sums[NT];
+                        for (int j = 0; j < TB / 4; ++j) w[j] = t0 + 4 * j < p.M ? __ldcg(mine + (t0 / 4 + j) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                    for (int j = 0; j < NT / 4; ++j) sums[4 * j] = w[j].x, sums[4 * j + 1] = w[j].y, sums[4 * j + 2] = w[j].z, sums[4 * j + 3] = w[j].w;
-                    store_outputs<NT>(p, sums, ss, quarter, lane);
+                        for (int j = 0; j < TB / 4; ++j)
+                            if (t0 + 4 * j < p.M) __stcg(mine + (t0 / 4 + j) * 32, make_float4(0.f, 0.f, 0.f, 0.f));
+                        float sums[TB];
+#pragma unroll
+                        for (int j = 0; j < TB / 4; ++j) sums[4 * j] = w[j].x, sums[4 * j + 1] = w[j].y, sums[4 * j + 2] = w[j].z, sums[4 * j + 3] = w[j].w;
+                        store_outputs<TB>(p, sums, t0, ss, quarter, lane);
+                    }
                     if (lane == 0) *counter = 0u;
                 }
             }
-            ++seg;
             seg_ch0 = -1;
             W4_TRACE();  // + 2: stored or reduced and completed
         }
@@ -551,7 +578,7 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
     umma::fence_before_sync();
     __syncthreads();
     W4_TRACE();  // CTA finished
-    if (warp == kMmaWarp) umma::tmem_dealloc(tmem_base, kTmemColsT);
+    if (warp == kMmaWarp0) umma::tmem_dealloc(tmem_base, kTmemColsT);
 }
 
 // Re-orders the 8-byte pieces of every 128-byte unit row: destination piece 4 r + c (MMA step r,
@@ -574,7 +601,7 @@ int launch_w4_tmem(const void* A, W4TmemParams p, DeviceState* dev, cudaStream_t
     using L = W4TmemSmem<NT, ASYM>;
     static_assert(L::kTotal <= 227 * 1024, "w4 tmem kernel exceeds shared memory");
     static_assert(L::kSlotBytes % 16 == 0 && (NT * 128) % 1024 == 0, "slot alignment");
-    static_assert(2 * NT <= kWeightCol0 && kWeightCol0 + kChunkStages * 128 <= kTmemColsT, "TMEM column budget");
+    static_assert(kSets * acc_bufs<NT>() * NT <= kWeightCol0 && kWeightCol0 + kChunkStages * 128 <= kTmemColsT, "TMEM column budget");
     const int chunks16 = p.M * (p.K / 8);
     SPK_CUDA(launch_chained(w4_permute_acts_kernel, dim3(cdiv(chunks16, 256)), dim3(256), 0, stream, static_cast<const uint2*>(A),
                             reinterpret_cast<uint4*>(dev->act_scratch), chunks16));

@@ -61,6 +61,7 @@ def kernel_for(m: int) -> str:
 
 # DRAM bytes moved per algorithmic byte, from one ncu capture per kernel (dram__bytes_read.sum +
 # dram__bytes_write.sum over the launch's algorithmic bytes; the captures are summarised under profiles/).
+EXPERTS = 8   # experts of the grouped fp8 GEMM rows (--kind grouped)
 NCU_TRAFFIC_RATIO = {"w4_tmem_kernel": 1.033, "w4_stream_kernel": 1.005}
 
 
@@ -577,15 +578,51 @@ def run_ours(args) -> None:
 
 
 def time_one_gemm(kind: str, d0: int, d1: int, d2: int, steps: int, use_graph: bool) -> dict:
-    """A small case for ncu and for the secondary GEMMs: one shape through the public op, a few
+    """A small case for ncu and for the secondary rows: one shape through the public op, a few
     launches, timed with CUDA events. w4: K,N,M over 4 weight copies (larger than L2 together for the
-    Llama shapes). fp8 / fp8block / mxfp8 / nvfp4 / mxfp4: M,N,K (weights rotated past L2 when M <= 64)."""
+    Llama shapes); w4swiglu: the same through the fused gate|up + SwiGLU launch (N = 2 x intermediate).
+    fp8 / fp8block / mxfp8 / nvfp4 / mxfp4: M,N,K (weights rotated past L2 when M <= 64). grouped: T,N,K over
+    EXPERTS equal experts. quant-w4: K,N of a bf16 weight; quant-fp8row / quant-fp8mx / quant-fp4: rows,K
+    of a bf16 matrix (the third number is ignored), rate = bytes read + written."""
     import torch
 
     import spark_kernels as sk
 
     g = torch.Generator(device="cuda").manual_seed(0)
-    if kind == "w4":
+    stream_bytes = None
+    if kind.startswith("quant-"):
+        rows, cols = d0, d1
+        x = (torch.randn(rows, cols, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+        if kind == "quant-w4":      # [K, N] weight -> int4 codes (half a byte) + a bf16 scale per 128 k
+            calls, out_bytes = [lambda: sk.w4_quantize(x)], rows * cols * (0.5 + 2 / 128)
+        elif kind == "quant-fp8row":
+            calls, out_bytes = [lambda: sk.fp8_quantize(x, "row")], rows * cols + 4 * rows
+        elif kind == "quant-fp8mx":
+            calls, out_bytes = [lambda: sk.fp8_quantize(x, "mx")], rows * cols * (1 + 1 / 32)
+        else:
+            sc = torch.tensor(0.01, device="cuda")
+            calls, out_bytes = [lambda: sk.fp4_quantize(x, "nvfp4", sc)], rows * cols * (0.5 + 1 / 16)
+        work, unit = 2 * rows * cols + out_bytes, "GB/s"
+    elif kind == "grouped":
+        T, N, K, E = d0, d1, d2, EXPERTS
+        a = torch.randn(T, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
+        w = (torch.randn(E, N, K, device="cuda", generator=g) * 0.05).to(torch.float8_e4m3fn)
+        off = torch.tensor([T * e // E for e in range(E + 1)], dtype=torch.int32, device="cuda")
+        sa, sb = torch.ones(1, device="cuda"), torch.ones(E, device="cuda")
+        calls = [lambda: sk.grouped_gemm_fp8(a, w, off, sa, sb)]
+        work, unit = 2 * T * N * K, "TFLOP/s"
+        stream_bytes = T * K + E * N * K + 2 * T * N
+    elif kind == "w4swiglu":
+        K, N, M = d0, d1, d2
+        ws = []
+        for _ in range(4):
+            wq = sk.W4GateUpWeight.quantize((torch.randn(K, N, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+            ws.append(wq)
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        calls = [lambda i=i: sk.w4gemm_swiglu(a, ws[i], out) for i in range(4)]
+        work, unit = alg_bytes(M, N, K) - M * N, "GB/s"   # half the output bytes of the plain GEMM
+    elif kind == "w4":
         K, N, M = d0, d1, d2
         ws = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 16, 2 * K), dtype=torch.int32, device="cuda", generator=g),
                (torch.rand(K // 128, N, device="cuda", generator=g) * 0.02).to(torch.bfloat16)) for _ in range(4)]
@@ -656,7 +693,7 @@ def time_one_gemm(kind: str, d0: int, d1: int, d2: int, steps: int, use_graph: b
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / n
     rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-    extra = {} if kind == "w4" else {"gbps": round(stream_bytes / (ms * 1e-3) / 1e9, 1)}
+    extra = {} if stream_bytes is None else {"gbps": round(stream_bytes / (ms * 1e-3) / 1e9, 1)}
     return {"one_gemm": [d0, d1, d2], "kind": kind, "launches": 3 + n, "us_per_launch": round(ms * 1e3, 2),
                       "rate": round(rate, 1), "unit": unit, **extra, "timing": timing,
                       "status": sk._C.device_status()}
@@ -694,6 +731,27 @@ def secondary_gemms() -> list:
         r = time_one_gemm(kind, 16, 4096, 4096, 40, True)
         rows.append({"kind": kind, "shape": [16, 4096, 4096], "us": r["us_per_launch"], "gbps": r["gbps"],
                      "frac": round(r["gbps"] / hbm, 3), "peak": "hbm", "timing": r["timing"]})
+    # int4 with many tokens (dequantize once + dense bf16 tcgen05 GEMM), against the bf16 peak
+    K, N, M = 4096, 28672, 2048
+    r = time_one_gemm("w4", K, N, M, 20, False)
+    tf = 2.0 * M * N * K / (r["us_per_launch"] * 1e-6) / 1e12
+    rows.append({"kind": "w4_prefill", "shape": [M, N, K], "us": r["us_per_launch"], "tflops": round(tf, 1), "launches": 20,
+                 "frac": round(tf / bf16, 3), "peak": f"{src}1 (burst)",
+                 "frac_sustained": None if sustained is None else round(tf / sustained, 3), "timing": r["timing"]})
+    # the fused gate|up + SwiGLU launch at 64 tokens, as a weight stream
+    r = time_one_gemm("w4swiglu", 4096, 28672, 64, 40, True)
+    rows.append({"kind": "w4_gate_up_swiglu", "shape": [64, 28672, 4096], "us": r["us_per_launch"], "gbps": r["rate"],
+                 "frac": round(r["rate"] / hbm, 3), "peak": "hbm", "timing": r["timing"]})
+    # grouped fp8 GEMM: 8 experts x 512 tokens of a 4096 -> 28672 expert projection, one launch
+    r = time_one_gemm("grouped", 4096, 28672, 4096, 20, False)
+    rows.append({"kind": "grouped_fp8", "experts": EXPERTS, "shape": [4096, 28672, 4096], "us": r["us_per_launch"], "tflops": r["rate"],
+                 "launches": 20, "frac": round(r["rate"] / (2 * bf16), 3), "peak": f"{src}2 (burst)",
+                 "frac_sustained": None if sustained is None else round(r["rate"] / (2 * sustained), 3), "timing": r["timing"]})
+    # quantizers and the packer's front end, as streams (bytes read + written)
+    for kind, shape in (("quant-w4", (4096, 28672)), ("quant-fp8row", (8192, 8192)), ("quant-fp4", (8192, 8192))):
+        r = time_one_gemm(kind, shape[0], shape[1], 0, 20, False)
+        rows.append({"kind": kind, "shape": list(shape), "us": r["us_per_launch"], "gbps": r["rate"],
+                     "frac": round(r["rate"] / hbm, 3), "peak": "hbm", "timing": r["timing"]})
     return rows
 
 
@@ -708,8 +766,9 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline and the secondary (fp8 / fp4) legs")
     ap.add_argument("--one-gemm", default="", metavar="A,B,C",
                     help="profiling helper: run --steps launches of one GEMM shape through the public op and exit")
-    ap.add_argument("--kind", default="w4", choices=["w4", "fp8", "fp8block", "mxfp8", "nvfp4", "mxfp4"],
-                    help="with --one-gemm: which GEMM (w4 takes K,N,M; the others M,N,K)")
+    ap.add_argument("--kind", default="w4", choices=["w4", "w4swiglu", "fp8", "fp8block", "mxfp8", "nvfp4", "mxfp4", "grouped",
+                                                     "quant-w4", "quant-fp8row", "quant-fp8mx", "quant-fp4"],
+                    help="with --one-gemm: which op (w4, w4swiglu take K,N,M; grouped T,N,K; quant-* rows,cols,0; the others M,N,K)")
     ap.add_argument("--graph", action="store_true", help="with --one-gemm: time the launches inside one CUDA graph")
     args = ap.parse_args()
     if args.one_gemm:
