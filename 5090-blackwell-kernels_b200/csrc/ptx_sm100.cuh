@@ -59,6 +59,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
     return ok != 0;
 }
 
+// Non-blocking probe: true if the phase has completed. Its result comes back through the scoreboard, so
+// a probe issued before a stretch of arithmetic costs nothing if the answer is used only afterwards.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Limit of one wait, in SM clock cycles: about a second at 2 GHz, far beyond any healthy copy or MMA
 // (and beyond a chained launch's wait for the kernel in front), and short enough that a broken
 // pipeline returns instead of hanging the GPU. The limit is a time, not a number of tries, because

@@ -49,6 +49,7 @@ using ptx::bulk_g2s;
 using ptx::mbar_arrive;
 using ptx::mbar_arrive_expect_tx;
 using ptx::mbar_init;
+using ptx::mbar_test_wait;
 using ptx::mbar_wait;
 
 constexpr int kStrips = 8;        // 16-column strips per super-strip
@@ -313,13 +314,21 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
         const int n_mine = n_chunks > set ? (n_chunks - set + 1) / 2 : 0;
         int slot_i = 0, cs = set, bi = set;  // chunk stage and barrier index of the chunks visited set-th, (set + 2)-th, ...
         unsigned code_ph = 0, bph = 0;
-        bool ok = true, chained = false;
+        // A barrier wait costs this warp ~300 cycles even when the phase has long completed (the round trip of the
+        // test through the shared-memory pipe). The waits of an iteration are therefore probed early, without
+        // blocking (the next chunk's codes at the end of the iteration before, the TMEM stage before the first
+        // group's arithmetic), and the blocking wait runs only if the probe said no.
+        bool ok = true, chained = false, codes_in = false;
         int it = 0;
         for (; it < n_mine && ok; ++it) {
             W4_TRACE();  // dequant 2 + 5 it: iteration start
-            ok = __all_sync(0xffffffffu, mbar_wait(&my_bar[slot_i], code_ph, p.status));
+            if (!codes_in) ok = __all_sync(0xffffffffu, mbar_wait(&my_bar[slot_i], code_ph, p.status));
             if (!ok) break;
             W4_TRACE();  // + 1: codes landed
+            const bool reused = set + kSets * it >= kChunkStages;  // the stage was used before: wait for those MMAs
+            uint64_t* free_bar = &a_free[bi >= kChunkStages ? bi - kChunkStages : bi + kChunkStages];
+            const unsigned free_ph = bi >= kChunkStages ? bph : bph ^ 1u;  // chunk j - 3: barrier (j - 3) % 6, phase (j - 3) / 6
+            const bool free_early = reused ? mbar_test_wait(free_bar, free_ph) : true;
             const unsigned char* slot = ring + slot_i * L::kSlotBytes;
             const uint4* cw = reinterpret_cast<const uint4*>(slot);
 #pragma unroll
@@ -346,14 +355,12 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
                     // the MMA warp, which needs activations that exist only once the kernel in front of a
                     // chained launch has completed: wait for that first, so that the poll budget below
                     // measures this kernel's pipeline and not how long the predecessor still runs.
-                    if (!chained && set + kSets * it >= kChunkStages) {
+                    if (!chained && reused) {
                         pdl_wait();
                         chained = true;
                     }
                     W4_TRACE();  // + 2: first group dequantized
-                    // chunk j waits for the MMAs of chunk j - 3: barrier (j - 3) % 6, its phase (j - 3) / 6
-                    ok = __all_sync(0xffffffffu, mbar_wait(&a_free[bi >= kChunkStages ? bi - kChunkStages : bi + kChunkStages],
-                                                           bi >= kChunkStages ? bph : bph ^ 1u, p.status));
+                    if (!__all_sync(0xffffffffu, free_early)) ok = __all_sync(0xffffffffu, mbar_wait(free_bar, free_ph, p.status));
                     if (!ok) break;
                     umma::fence_after_sync();
                     W4_TRACE();  // + 3: TMEM stage free
@@ -375,10 +382,11 @@ __global__ void __launch_bounds__(kThreadsT, 1) w4_tmem_kernel(const __grid_cons
             __syncwarp();
             issue();
             if (++slot_i == kCodeSlots) slot_i = 0, code_ph ^= 1u;
+            const bool next_codes = it + 1 < n_mine && mbar_test_wait(&my_bar[slot_i], code_ph);
             W4_TRACE();  // + 4: stores issued, next copy requested
             tmem_st_wait();
             umma::fence_before_sync();
-            __syncwarp();
+            codes_in = __all_sync(0xffffffffu, next_codes);
             if (lane == 0) mbar_arrive(&a_ready[bi]);
             cs += kSets;
             if (cs >= kChunkStages) cs -= kChunkStages;
