@@ -8,9 +8,11 @@
 // Buffer of one rank (the same layout on all, allocated by spk_comm_alloc, opened by the peers
 // through CUDA IPC):
 //   [0, 1024)      arrival counters, one pair per source rank, 128 bytes apart; they only ever grow:
-//                  every call adds kCtas per source to the first, and call number q waits for
-//                  kCtas * (q + 1); two-phase calls add kCtas to the second (at +64) as well
-//   [1024, 1044)   call counter, finished-CTA counter, status word, two-phase call counter
+//                  every call of a counter form adds kCtas per source to the first, and the c-th such
+//                  call waits for kCtas * (c + 1); two-phase calls add kCtas to the second (at +64) as well
+//   [1024, 1048)   call counter (all forms: selects the half and the flagged words' sequence number),
+//                  finished-CTA counter, status word, two-phase call counter, counter-form call counter
+//                  (flagged calls raise no arrival counter, so the counter forms count their own calls)
 //   [4096, ...)    slots [2][world][slot_elems] bf16, then the flagged inboxes [2][2][slot_elems / 2] cells; call q uses half q % 2, so a rank that is one
 //                  call ahead never writes where a slower peer still reads (it cannot be two ahead:
 //                  finishing call q + 1 needs the peer's arrival for q + 1, which the peer raises only
@@ -72,6 +74,8 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_push_kernel(const Comm
     unsigned* done_ptr = seq_ptr + 1;
     int* status = reinterpret_cast<int*>(seq_ptr + 2);
     const unsigned seq = *reinterpret_cast<volatile unsigned*>(seq_ptr);  // advanced only after every CTA has finished
+    unsigned* cnt1_ptr = seq_ptr + 4;  // calls that raised the first arrival counter (one phase, two phases)
+    const unsigned cnt1 = *reinterpret_cast<volatile unsigned*>(cnt1_ptr);
     const unsigned half = seq & 1u;
     const long long vecs = p.n / 8;  // 16-byte vectors
     const long long v0 = vecs * blockIdx.x / gridDim.x, v1 = vecs * (blockIdx.x + 1) / gridDim.x;
@@ -179,7 +183,7 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_push_kernel(const Comm
             }
             __syncthreads();
         };
-        wait_all(0, static_cast<unsigned>(gridDim.x) * (seq + 1u));
+        wait_all(0, static_cast<unsigned>(gridDim.x) * (cnt1 + 1u));
         // ---- phase 2: sum the world slots of this CTA's share of the local slice in rank order, keep it, and
         // store it into the second region of every peer ----
         if (!failed2) {
@@ -226,6 +230,7 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_push_kernel(const Comm
             if (atomicAdd(done_ptr, 1u) == gridDim.x - 1) {
                 *done_ptr = 0u;
                 *reinterpret_cast<volatile unsigned*>(seq2_ptr) = seq2 + 1u;
+                *reinterpret_cast<volatile unsigned*>(cnt1_ptr) = cnt1 + 1u;
                 __threadfence();
                 *reinterpret_cast<volatile unsigned*>(seq_ptr) = seq + 1u;
             }
@@ -253,7 +258,7 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_push_kernel(const Comm
     __syncthreads();
     if (threadIdx.x < p.world) {
         const unsigned* flag = reinterpret_cast<const unsigned*>(local + kCommFlagStride * threadIdx.x);
-        const unsigned target = static_cast<unsigned>(gridDim.x) * (seq + 1u);
+        const unsigned target = static_cast<unsigned>(gridDim.x) * (cnt1 + 1u);
         bool ok = false;
         for (unsigned i = 0; i < kCommPolls && !ok; ++i) {
             ok = static_cast<int>(ld_acquire_sys(flag) - target) >= 0;  // counters wrap together
@@ -295,6 +300,7 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_push_kernel(const Comm
         __threadfence();
         if (atomicAdd(done_ptr, 1u) == gridDim.x - 1) {
             *done_ptr = 0u;
+            *reinterpret_cast<volatile unsigned*>(cnt1_ptr) = cnt1 + 1u;
             __threadfence();
             *reinterpret_cast<volatile unsigned*>(seq_ptr) = seq + 1u;
         }

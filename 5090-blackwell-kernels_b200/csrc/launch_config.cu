@@ -9,7 +9,9 @@
 //   [split, 2 split] whose last wave is >= 87.5% full, else the fullest
 //   a forced split (decode_force_split_k / SPARK_DECODE_SPLIT) replaces the rule.
 // Named shapes make the rule testable without a GPU: the two the reference names (GB10, RTX 5090)
-// with its constants, and B200 (148 SMs, 126 MB L2, 8 TB/s HBM3e, 1 us loaded latency).
+// with its constants, and B200 (148 SMs, 126 MB L2, 7.7 TB/s HBM3e nominal) with the bytes in flight MEASURED here:
+// a read-only stream of bulk copies (spk_stream_probe) reaches ~6 TB/s once ~10 MB are outstanding over the
+// device (6.5 TB/s x ~1.5 us loaded latency) and 7.2 TB/s with more; less in flight leaves bandwidth unused.
 #include <algorithm>
 #include <atomic>
 #include <cstdlib>
@@ -29,7 +31,7 @@ struct Shape {
 
 constexpr Shape kGB10 = {48, int64_t{24} << 20, 273.0, 273 * 800, false};
 constexpr Shape kRTX5090 = {170, int64_t{96} << 20, 1792.0, int64_t{64} * 24 * 1024, false};
-constexpr Shape kB200 = {148, int64_t{126} << 20, 8000.0, 8000 * 1000, false};
+constexpr Shape kB200 = {148, int64_t{126} << 20, 7700.0, int64_t{10} << 20, false};
 constexpr double kL2ResidentShare = 0.75;
 
 std::atomic<int> g_forced_split{-1};  // -1: SPARK_DECODE_SPLIT not read yet
@@ -66,7 +68,8 @@ Shape current_shape() {
         cudaDeviceGetAttribute(&width, cudaDevAttrGlobalMemoryBusWidth, dev) == cudaSuccess && clk > 0 && width > 0)
         s.spec_gbps = 2.0 * clk * 1e3 * (width / 8.0) / 1e9;
     (void)cudaGetLastError();
-    s.bytes_in_flight = static_cast<int64_t>(s.spec_gbps * 1000.0);  // 1 us loaded latency
+    // the measured B200 figure scaled by the bandwidth this device reports (1.3 us of its nominal rate)
+    s.bytes_in_flight = static_cast<int64_t>(static_cast<double>(kB200.bytes_in_flight) * s.spec_gbps / kB200.spec_gbps);
     const int forced = env_int("SPARK_FORCE_SMS");
     if (forced > 0) {
         s.sm_count = forced;

@@ -77,7 +77,7 @@ def test_fits_l2_other_shapes_and_errors():
     # B200: the whole int4 gate|up weight (57.75 MB) stays L2 resident, the bf16 one does not
     assert _C.fits_l2(4096 * 28672 // 2 + 32 * 28672 * 2, "b200")
     assert not _C.fits_l2(4096 * 28672 * 2, "b200")
-    assert _C.need_ctas(8192, "b200") == cdiv(8000 * 1000, 8192)
+    assert _C.need_ctas(8192, "b200") == cdiv(10 * MB, 8192)   # 10 MiB in flight, measured with the stream probe
     with pytest.raises((ValueError, RuntimeError)):
         _C.fits_l2(1, "h100")
 
