@@ -120,24 +120,24 @@ __device__ __forceinline__ void store_outputs(const W4TmemParams& p, const float
         return;
     }
     const int half_n = p.N / 2, col = ss * 64 + quarter * 16 + (lane & 15);
-    // Lanes 0-15 hold the gate sums of 16 outputs, lanes 16-31 the matching up sums. The lower half takes tokens
-    // t, the upper half tokens t + TB / 2: one exchange per token pair gives each its missing operand (the lower half
-    // sends the gate of t + TB / 2 and receives the up of t, the upper half the other way round), so all 32 lanes do
-    // useful arithmetic and stores. This warp's tail is on the critical path of the launch: with the arithmetic only
-    // on the lower half (and, before that, under a divergent branch) the fused form cost 7 us more at 64 tokens.
+    // (A form in which the upper half-warp takes half of the tokens through one exchange per token pair halves this
+    // arithmetic and brought the fused launch from 36.5 to 35.0 us at 64 tokens, but the plain kernel, which shares
+    // this kernel's register allocation and schedule, then ran 6 % slower at 64 tokens, 24.7 -> 26.2 us; making the
+    // epilogue a template parameter or an out-of-line function was slower still. Not kept.)
+    // Every lane computes (the upper half's results are unused): with the arithmetic under the `lane < 16` branch the
+    // shuffle -> exp -> reciprocal chains ran one after another, ~100 cycles each, on this warp's tail.
     // Hardware exp2 / reciprocal: a few ulp of fp32, far below the bf16 rounding of the result.
-    const bool low = lane < 16;
-    __nv_bfloat16 h[TB / 2];
+    __nv_bfloat16 h[TB];
 #pragma unroll
-    for (int t = 0; t < TB / 2; ++t) {
-        const float got = __shfl_xor_sync(0xffffffffu, low ? v[t + TB / 2] : v[t], 16);
-        const float gate = low ? v[t] : got, up = low ? got : v[t + TB / 2];
+    for (int t = 0; t < TB; ++t) {
+        const float up = __shfl_down_sync(0xffffffffu, v[t], 16), gate = v[t];
         h[t] = __float2bfloat16_rn(__fdividef(gate, 1.0f + __expf(-gate)) * up);
     }
-    const int tok0 = t0 + (low ? 0 : TB / 2);
+    if (lane < 16) {
 #pragma unroll
-    for (int t = 0; t < TB / 2; ++t)
-        if (tok0 + t < p.M) p.C[static_cast<size_t>(tok0 + t) * half_n + col] = h[t];
+        for (int t = 0; t < TB; ++t)
+            if (t0 + t < p.M) p.C[static_cast<size_t>(t0 + t) * half_n + col] = h[t];
+    }
 }
 
 template <int NT, bool ASYM>
