@@ -673,7 +673,8 @@ def comm_status(local_ptr: int) -> int:
 
 def allreduce_push(t: torch.Tensor, ptrs, rank: int, slot_elems: int, mode: int = 0) -> torch.Tensor:
     """In-place sum of the contiguous bf16 tensor t over the ranks whose buffers are `ptrs`.
-    mode 0: the library picks the form, 1: one phase, 2: two phases (reduce-scatter + all-gather)."""
+    mode 0: the library picks the form, 1: one phase, 2: two phases (reduce-scatter + all-gather), 3: two phases of
+    flagged words, 4: one hop of flagged words."""
     _check_cuda_contig(t, "t")
     _check(t.dtype == torch.bfloat16, "allreduce_push: bf16 only")
     arr = (_p * len(ptrs))(*ptrs)

@@ -177,8 +177,9 @@ class PushAllReduce:
         self.local, self.ptrs = 0, []
 
     def __call__(self, t: torch.Tensor, mode: int = 0) -> torch.Tensor:
-        """mode 0: the library picks one phase (every rank stores its tensor into every peer) or two
-        (reduce-scatter + all-gather by peer stores, for large tensors on four ranks and more); 1 / 2 force one."""
+        """mode 0: the library picks the form (one hop of flagged words up to four ranks, two phases of flagged words
+        beyond); 1 one phase with arrival counters, 2 two phases with counters, 3 two phases of flagged words, 4 one
+        hop of flagged words."""
         return self._C.allreduce_push(t, self.ptrs, self.rank, self.slot_elems, mode)
 
     def status(self) -> int:

@@ -273,7 +273,7 @@ def run_ours(args) -> None:
                 def reduce(t, _p=pusher):
                     return _p(t)
 
-                reduce_name = "push (peer stores over NVLink, one kernel per rank; two-phase from 4 ranks and 128 KiB up)"
+                reduce_name = "push (flagged peer stores over NVLink, one kernel per rank; one hop while (world - 1) x the doubled tensor is within 1 MiB, two phases beyond)"
             except Exception as e:  # CUDA IPC can be closed to a container; NCCL then carries the sum
                 reduce_name = f"nccl (push unavailable: {type(e).__name__})"
             ok_all = torch.tensor([1.0 if reduce_name.startswith("push") else 0.0], device=dev)

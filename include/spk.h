@@ -228,7 +228,8 @@ SPK_API int spk_allreduce_push_bf16(void* data, long long n, void* const* bufs, 
 /* The same sum with the form forced: mode 1 one phase (every rank stores its whole tensor into every
  * peer), mode 2 two phases (reduce-scatter then all-gather by peer stores and arrival counters), mode 3
  * the two phases with the sequence number travelling inside every 8-byte store (no fence, no counter:
- * the lowest latency), mode 0 what spk_allreduce_push_bf16 picks. Modes 2 and 3 need n % (8 world) == 0.
+ * the lowest latency), mode 4 one hop of such flagged words (the whole tensor to every peer, summed where it lands:
+ * what two to four ranks get by default), mode 0 what spk_allreduce_push_bf16 picks. Modes 2 and 3 need n % (8 world) == 0.
  * Identical bits on every rank in all forms; they may be mixed as long as all ranks make the same calls. */
 SPK_API int spk_allreduce_push_bf16_mode(void* data, long long n, void* const* bufs, int rank, int world,
                                          long long slot_elems, int mode, void* stream);

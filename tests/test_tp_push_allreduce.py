@@ -33,7 +33,7 @@ for n in (8, 4096, 16 * 4096, 64 * 4096):
         torch.cuda.synchronize()
         assert torch.equal(got, want.to(torch.bfloat16)), (n, rep)
         if n % (8 * world) == 0:   # the two-phase form (reduce-scatter + all-gather), forced, interleaved with the other
-            for mode in (2, 3, 1, 3):
+            for mode in (2, 3, 4, 1, 3, 4):
                 got2 = ar(x.clone(), mode=mode)
                 torch.cuda.synchronize()
                 assert torch.equal(got2, want.to(torch.bfloat16)), ("mode", mode, n, rep)
