@@ -234,9 +234,11 @@ def tp_check(sk, dist, dev, rank, tp, reducers) -> dict:
         torch.cuda.synchronize()
         ok, err = close(y, want)
         res[f"down_allreduce_{name}"] = {"ok": ok, "max_err_over_max": round(err, 5)}
-    flag = torch.tensor([1.0 if all(v["ok"] for v in res.values()) else 0.0], device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    res["status"] = "ok" if flag.item() >= 1.0 else "FAILED"
+    flags = torch.tensor([1.0 if all(v["ok"] for v in res.values()) else 0.0,
+                          1.0 if all(v["ok"] for k, v in res.items() if k != "down_allreduce_push") else 0.0], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    res["status"] = "ok" if flags[0].item() >= 1.0 else "FAILED"
+    res["status_without_push"] = "ok" if flags[1].item() >= 1.0 else "FAILED"  # the same on every rank
     return res
 
 
@@ -286,6 +288,11 @@ def run_ours(args) -> None:
         if reduce_name.startswith("push"):
             reducers["push"] = lambda t, _p=pusher: _p(t)
         tp_res = tp_check(sk, dist, dev, rank, tp, reducers)
+        if tp_res["status"] != "ok" and tp_res["status_without_push"] == "ok":
+            # only the push all-reduce disagrees with the unsharded GEMM: time with NCCL (checked above) and say so
+            reduce, reduce_name = (lambda t: dist.all_reduce(t)), "nccl (the push all-reduce failed the check against the unsharded GEMM)"
+            tp_res["status"] = "ok"
+            tp_res["note"] = "push all-reduce failed the check; NCCL is what is timed"
         if tp_res["status"] != "ok":
             if rank == 0:
                 print(json.dumps({"metric": "int4_decode_gemm_gbps", "value": None, "n_gpus": world, "tp_check": tp_res}), flush=True)
