@@ -5,10 +5,9 @@
 //
 // Compared with staging the dequantized weights in shared memory this drops the 16-byte shared
 // stores, their bank traffic and the generic->async proxy fence from the dequant warps (a
-// tcgen05.st plus tcgen05.wait::st takes their place), and it frees 96 KiB of shared memory, which
-// goes into deeper code rings. TMEM also holds six 128-k groups of weights instead of three, so a
-// dequant warp can take a whole 2-group chunk (one 2 KiB bulk copy, one barrier wait, one hand-off)
-// per iteration.
+// tcgen05.st plus tcgen05.wait::st takes their place), and it frees 96 KiB of shared memory. TMEM
+// also holds six 128-k groups of weights instead of three, so a dequant warp can take a whole
+// 2-group chunk (one 2 KiB bulk copy, one barrier wait, one hand-off) per iteration.
 //
 // A dequant lane (g, c) of the packed layout holds, for columns g and g + 8 of its strip, the k
 // quads 8c + 4(r & 1) + 32(r >> 1) + {0..3}, r = 0..3, of a 64-k unit. tcgen05.st.16x256b places
