@@ -5,9 +5,12 @@
 //
 // Quantizer: one CTA per (128-k group, 128 columns). The TMA engine brings the 128 x 128 bf16 tile
 // into shared memory with one bulk copy per k row (256 contiguous bytes each, all on one mbarrier),
-// so W is read from HBM exactly once, in full rows. Two threads share a column (64 k each): they
-// reduce min / max / |max| from shared memory, exchange them, derive scale and zero point, and each
-// emits its 8 GPTQ words; a warp's stores of one k-octet are 128 contiguous bytes.
+// so W is read from HBM exactly once, in full rows. A thread takes two adjacent columns (one 32-bit
+// shared-memory load gives both, and min / max / |max| run as packed bf16 operations) and a quarter of
+// the k range; the four quarters exchange their ranges through shared memory, every thread derives the
+// scale and zero point of its two columns and emits its four GPTQ words of each; a warp's stores of one
+// k-octet are 256 contiguous bytes. The per-weight division of the definition is replaced by a
+// multiplication with the reciprocal plus an exact treatment of ties (see the kernel).
 //
 // Repack: a warp per 512-byte output block (16 columns x 64 k). Its 8 x 16 source words arrive as one
 // 16-byte load per lane and are staged in shared memory; each lane then builds its four output
@@ -25,16 +28,12 @@ namespace {
 constexpr int kQCols = 128;     // columns per quantizer CTA
 constexpr int kQThreads = 256;  // two threads per column
 
-struct ColumnRange {
-    float lo, hi, amax;
-};
-
 template <bool ASYM>
 __global__ void __launch_bounds__(kQThreads)
 w4_quantize_tile_kernel(const __nv_bfloat16* __restrict__ W, uint32_t* __restrict__ qweight,
                         __nv_bfloat16* __restrict__ scales, uint8_t* __restrict__ zeros, int N, int bulk, int* status) {
     __shared__ __align__(128) __nv_bfloat16 tile[w4::kGroup][kQCols];
-    __shared__ ColumnRange other[kQCols];  // the upper half's range of every column
+    __shared__ uint3 quarter_range[4][kQCols / 2];  // (min, max, |max|) of a column pair over one k quarter, as bf16 pairs
     __shared__ uint64_t bar;
     const int n0 = blockIdx.x * kQCols, g = blockIdx.y;
     const int cols = min(kQCols, N - n0);  // a multiple of 16
@@ -63,58 +62,84 @@ w4_quantize_tile_kernel(const __nv_bfloat16* __restrict__ W, uint32_t* __restric
         __syncthreads();
     }
 
-    const int col = threadIdx.x & (kQCols - 1), half = threadIdx.x >> 7;
-    const int k0 = half * (w4::kGroup / 2);
-    ColumnRange r = {0.f, 0.f, 0.f};
-    if (col < cols) {
-#pragma unroll 16
-        for (int k = 0; k < w4::kGroup / 2; ++k) {
-            const float w = __bfloat162float(tile[k0 + k][col]);
-            r.lo = fminf(r.lo, w);
-            r.hi = fmaxf(r.hi, w);
-            r.amax = fmaxf(r.amax, fabsf(w));
+    // A thread takes two adjacent columns (one 32-bit shared-memory load gives both) and a quarter of the k range.
+    const int cp = threadIdx.x & 63, kq = threadIdx.x >> 6;   // column pair, k quarter (32 k)
+    const int k0 = kq * (w4::kGroup / 4);
+    const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(&tile[0][0]) + cp;   // row pitch kQCols / 2 words
+    __nv_bfloat162 lo2 = __float2bfloat162_rn(0.f), hi2 = lo2, am2 = lo2;  // the ranges include 0, as the definition's do
+    if (2 * cp < cols) {
+#pragma unroll 8
+        for (int k = 0; k < w4::kGroup / 4; ++k) {
+            const uint32_t u = tile32[(k0 + k) * (kQCols / 2)];
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&u);
+            lo2 = __hmin2(lo2, x), hi2 = __hmax2(hi2, x), am2 = __hmax2(am2, __habs2(x));
         }
     }
-    if (half == 1) other[col] = r;
+    quarter_range[kq][cp] = make_uint3(*reinterpret_cast<uint32_t*>(&lo2), *reinterpret_cast<uint32_t*>(&hi2), *reinterpret_cast<uint32_t*>(&am2));
     __syncthreads();
-    if (half == 0) {
-        const ColumnRange o = other[col];
-        r.lo = fminf(r.lo, o.lo), r.hi = fmaxf(r.hi, o.hi), r.amax = fmaxf(r.amax, o.amax);
-        other[col] = r;
+    if (2 * cp >= cols) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // every thread folds the four quarters itself: no second barrier
+        const uint3 o = quarter_range[j][cp];
+        lo2 = __hmin2(lo2, *reinterpret_cast<const __nv_bfloat162*>(&o.x));
+        hi2 = __hmax2(hi2, *reinterpret_cast<const __nv_bfloat162*>(&o.y));
+        am2 = __hmax2(am2, *reinterpret_cast<const __nv_bfloat162*>(&o.z));
     }
-    __syncthreads();
-    if (col >= cols) return;
-    r = other[col];
 
-    // fp32 throughout; the codes are computed against the bf16-rounded scale, the number the GEMM will
-    // multiply by, with IEEE division and round-half-even
-    const __nv_bfloat16 s_bf = __float2bfloat16_rn(ASYM ? __fdiv_rn(r.hi - r.lo, 15.0f) : __fdiv_rn(r.amax, 7.0f));
-    const float s = __bfloat162float(s_bf);
-    const bool live = s > 0.f;
-    float zf = 8.f, qmin = -8.f, qmax = 7.f, shift = 8.f;  // symmetric: q = clamp(rint(w / s), -8, 7) + 8
-    if (ASYM) {
-        zf = live ? fminf(fmaxf(rintf(__fdiv_rn(-r.lo, s)), 0.f), 15.f) : 0.f;
-        qmin = 0.f, qmax = 15.f, shift = 0.f;  // q = clamp(rint(w / s) + z, 0, 15)
+    // Per column, fp32 throughout: the codes are computed against the bf16-rounded scale, the number the GEMM will
+    // multiply by. The definition divides (IEEE) and rounds half to even. w and s are both bf16, so w / s is a ratio of
+    // two 8-bit integers times a power of two: unless it is exactly k + 1/2 it is at least 1 / 2040 away from every such
+    // tie, and w * (1 / s) lands within 3e-6 of it. So rint(w * r) is the definition's code except on exact ties, which
+    // show as a distance within 1e-4 of 1/2 and are then resolved to the even neighbour: no division per weight.
+    float s_col[2], r_col[2], z_col[2];
+    bool live_col[2], divide_col[2];  // divide: a scale so small that its reciprocal overflows keeps the division
+    __nv_bfloat16 sbf_col[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const float lo = c ? __high2float(lo2) : __low2float(lo2), hi = c ? __high2float(hi2) : __low2float(hi2);
+        const float amax = c ? __high2float(am2) : __low2float(am2);
+        sbf_col[c] = __float2bfloat16_rn(ASYM ? __fdiv_rn(hi - lo, 15.0f) : __fdiv_rn(amax, 7.0f));
+        s_col[c] = __bfloat162float(sbf_col[c]);
+        live_col[c] = s_col[c] > 0.f;
+        divide_col[c] = live_col[c] && s_col[c] < 1e-30f;
+        r_col[c] = live_col[c] && !divide_col[c] ? __frcp_rn(s_col[c]) : 0.f;
+        z_col[c] = 8.f;
+        if (ASYM) z_col[c] = live_col[c] ? fminf(fmaxf(rintf(__fdiv_rn(-lo, s_col[c])), 0.f), 15.f) : 0.f;
     }
-    const size_t n = static_cast<size_t>(n0) + col;
+    const float qmin = ASYM ? 0.f : -8.f, qmax = ASYM ? 15.f : 7.f;
+    // Rounding and the conversion to an integer go through the adder, not the conversion unit (rint and float -> int
+    // run at a quarter of the rate): x + 1.5 * 2^23 rounds x to an integer, half to even, for |x| < 2^22, and the
+    // integer then sits in the low mantissa bits.
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    auto code = [&](float w, int c) -> uint32_t {  // symmetric: clamp(rint(w / s), -8, 7) + 8; asym: clamp(rint(w / s) + z, 0, 15)
+        float rn, d;
+        if (divide_col[c]) {
+            const float t = __fdiv_rn(w, s_col[c]);
+            rn = rintf(t), d = t - rn;
+        } else {
+            rn = __fadd_rn(__fmaf_rn(w, r_col[c], kMagic), -kMagic);   // rint of the product
+            d = __fmaf_rn(w, r_col[c], -rn);                           // the product's distance from it
+            if (fabsf(fabsf(d) - 0.5f) < 1e-4f) rn = 2.0f * rintf(0.25f * rintf(2.0f * w * r_col[c]));  // an exact tie: the even neighbour
+        }
+        const float q = fminf(fmaxf(rn + (ASYM ? z_col[c] : 0.f), qmin), qmax) + (ASYM ? 0.f : 8.f);
+        const uint32_t bits = static_cast<uint32_t>(__float_as_int(q + kMagic)) & 0xFu;   // q is an integer in 0 .. 15
+        return live_col[c] ? bits : static_cast<uint32_t>(z_col[c]);
+    };
+    const size_t n = static_cast<size_t>(n0) + 2 * cp;
 #pragma unroll 2
-    for (int o = 0; o < w4::kGroup / 16; ++o) {  // this thread's eight k-octets
-        uint32_t word = 0;
+    for (int o = 0; o < w4::kGroup / 32; ++o) {  // this thread's four k-octets
+        uint32_t word0 = 0, word1 = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            float q = zf;
-            if (live) {
-                const float w = __bfloat162float(tile[k0 + 8 * o + i][col]);
-                const float t = rintf(__fdiv_rn(w, s)) + (ASYM ? zf : 0.f);
-                q = fminf(fmaxf(t, qmin), qmax) + shift;
-            }
-            word |= static_cast<uint32_t>(static_cast<int>(q)) << (4 * i);
+            const uint32_t u = tile32[(k0 + 8 * o + i) * (kQCols / 2)];
+            word0 |= code(__uint_as_float(u << 16), 0) << (4 * i);
+            word1 |= code(__uint_as_float(u & 0xFFFF0000u), 1) << (4 * i);
         }
-        qweight[(static_cast<size_t>(g) * (w4::kGroup / 8) + half * 8 + o) * N + n] = word;
+        *reinterpret_cast<uint2*>(qweight + (static_cast<size_t>(g) * (w4::kGroup / 8) + kq * 4 + o) * N + n) = make_uint2(word0, word1);
     }
-    if (half == 0) {
-        scales[static_cast<size_t>(g) * N + n] = s_bf;
-        if (ASYM) zeros[static_cast<size_t>(g) * N + n] = static_cast<uint8_t>(zf);
+    if (kq == 0) {
+        *reinterpret_cast<__nv_bfloat162*>(scales + static_cast<size_t>(g) * N + n) = __halves2bfloat162(sbf_col[0], sbf_col[1]);
+        if (ASYM) *reinterpret_cast<uchar2*>(zeros + static_cast<size_t>(g) * N + n) = make_uchar2(static_cast<uint8_t>(z_col[0]), static_cast<uint8_t>(z_col[1]));
     }
 }
 

@@ -32,6 +32,38 @@ def test_w4_quantize_matches_oracle(sk, orc, shape, asym):
         assert zeros is None
 
 
+@pytest.mark.parametrize("asym", [False, True], ids=["sym", "asym"])
+def test_w4_quantize_ties_and_extreme_scales_match_oracle(sk, orc, asym):
+    """The quantizer multiplies by the reciprocal of the scale and resolves exact ties itself instead of dividing:
+    columns made of exact ties (w / s = k + 1/2 for every k), of values one bf16 step either side of a tie, of
+    magnitudes from 1e-36 to 1e30, and random mantissas against every scale mantissa must give the oracle's codes."""
+    K, N = 256, 256
+    g = torch.Generator().manual_seed(5)
+    w = torch.zeros(K, N)
+    halves = torch.arange(-15, 16).float() * 0.5                      # -7.5 .. 7.5 in steps of 1/2: ties and integers
+    for n in range(N):
+        s0 = 2.0 ** ((n % 40) - 20) * (1 + (n % 7) / 8)               # scales with different mantissas and exponents
+        col = halves[torch.randint(0, len(halves), (K,), generator=g)] * s0
+        col[0], col[128] = 7 * s0, 7 * s0                             # |max| = 7 s0 in both groups: scale bf16(s0)
+        if n % 3 == 1:                                                # one bf16 step off the ties
+            bits = col.to(torch.bfloat16).view(torch.int16) + torch.randint(-1, 2, (K,), generator=g).to(torch.int16)
+            col = bits.view(torch.bfloat16).float()
+            col[0], col[128] = 7 * s0, 7 * s0
+        w[:, n] = col
+    w[:, 200:208] *= 1e-30                                            # scales whose reciprocal is huge
+    w[:128, 208:216] *= 1e-37
+    w[:, 216:224] *= 1e28
+    w[:, 224:] = (torch.randn(K, 32, generator=g) * torch.logspace(-3, 3, 32)).float()
+    w = w.to(torch.bfloat16)
+    qweight, scales, zeros = sk.w4_quantize(w.cuda(), asym=asym)
+    q_ref, s_ref, z_ref = orc.w4_quantize(t2n(w), asym=asym)
+    assert np.array_equal(t2n(scales), s_ref)
+    bad = np.argwhere(t2n(qweight) != q_ref)
+    assert bad.size == 0, f"{len(bad)} words differ, first at {bad[:3].tolist()}"
+    if asym:
+        assert np.array_equal(t2n(zeros), z_ref)
+
+
 @pytest.mark.parametrize("tag", ["sym", "asym"])
 def test_w4_quantize_and_repack_golden(sk, golden, tag):
     g = golden("w4")
