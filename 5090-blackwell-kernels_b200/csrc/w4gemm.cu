@@ -1,10 +1,10 @@
 // W4A16 GEMM: C[M,N] = A[M,K] * bf16((q - z) * s), int4 codes in the repacked layout, one bf16
 // scale (and optional zero point) per 128 k of a column, fp32 accumulation, bf16 out.
 // Contract: reference include/spark/kernels.h:366-416. Variants:
-//   0  one thread per output, scalar decode through w4::locate (the arithmetic of the
-//      reference's w4_naive_kernel, src/kernels/w4gemm.cu:46-67)
-//   1  one warp per 16-column strip and 8 tokens, codes and activations straight from global
-//      memory into registers, register dequant, warp-level MMA
+//   0  the plain rung, walking the packed layout: a CTA per (strip, token), every lane decodes its own 16-byte
+//      pieces nibble by nibble with scalar arithmetic, fixed-order sum through shared memory
+//   1  the first tensor-core rung: a CTA per (strip, 32 tokens), the strip's codes staged in shared memory by
+//      double-buffered bulk copies and shared by four warps with an 8-token tile each, register dequant, warp-level MMA
 //   2  (default) by token count: up to 16 tokens the B200 weight stream described next, up to a few hundred
 //      the tcgen05 kernel with the weights in TMEM (w4gemm_tmem.cu), above that dequantize once + dense
 //      bf16 tcgen05 GEMM (w4_prefill.cu). The weight stream: every warp owns a private ring of bulk asynchronous
@@ -37,25 +37,46 @@ using ptx::mbar_init;
 using ptx::mbar_wait;
 
 // ---- variant 0 ----------------------------------------------------------------------------------
-
-__global__ void w4_naive_kernel(const __nv_bfloat16* __restrict__ A, const uint32_t* __restrict__ packed,
-                                const __nv_bfloat16* __restrict__ scales, const uint8_t* __restrict__ zeros,
-                                __nv_bfloat16* __restrict__ C, int M, int N, int K) {
-    const int n = blockIdx.x * blockDim.x + threadIdx.x;
-    const int m = blockIdx.y;
-    if (n >= N || m >= M) return;
-    float acc = 0.f;
-    for (int k = 0; k < K; ++k) {
-        size_t word;
-        int p;
-        w4::locate(n, k, K, word, p);
-        const int q = (packed[word] >> (4 * p)) & 15;
-        const size_t si = static_cast<size_t>(k / w4::kGroup) * N + n;
-        const int z = zeros ? zeros[si] : 8;
-        const float w = __bfloat162float(__float2bfloat16_rn(static_cast<float>(q - z) * __bfloat162float(scales[si])));
-        acc = fmaf(__bfloat162float(A[static_cast<size_t>(m) * K + k]), w, acc);
+// The plain rung, organised by the PACKED layout rather than by output element: a CTA per (strip, token). Warp w walks
+// the strip's 64-k units w, w + 4, ...; a lane reads its own 16-byte piece of the unit (the piece of lane (g, c) holds
+// 16 k of columns g and g + 8), decodes the 32 codes one at a time with scalar arithmetic (w4::slot_source says which
+// column and k a nibble is) and accumulates the two columns' dot products in fp32. The 16 threads that hold the same
+// column pair are then summed in a fixed order through shared memory. No tensor cores, no asynchronous copies.
+__global__ void __launch_bounds__(128)
+w4_scalar_kernel(const __nv_bfloat16* __restrict__ A, const uint4* __restrict__ packed, const __nv_bfloat16* __restrict__ scales,
+                 const uint8_t* __restrict__ zeros, __nv_bfloat16* __restrict__ C, int M, int N, int K) {
+    __shared__ float part[128][2];
+    const int t = blockIdx.x, m = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
+    const int units = K / 64;
+    const __nv_bfloat16* a_row = A + static_cast<size_t>(m) * K;
+    float acc[2] = {0.f, 0.f};  // columns g and g + 8 of the strip
+    for (int u = warp; u < units; u += 4) {
+        const uint4 piece = packed[(static_cast<size_t>(t) * units + u) * 32 + lane];
+        const uint32_t words[4] = {piece.x, piece.y, piece.z, piece.w};
+        const size_t row = static_cast<size_t>(u >> 1) * N + 16 * t + g;  // the unit's group, this lane's first column
+        const float sc[2] = {__bfloat162float(scales[row]), __bfloat162float(scales[row + 8])};
+        const int zp[2] = {zeros ? zeros[row] : 8, zeros ? zeros[row + 8] : 8};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int nib = 0; nib < 8; ++nib) {
+                int dn, dk;
+                w4::slot_source(lane, u, j, nib, dn, dk);
+                const int hi = dn >> 3;  // 0: column g, 1: column g + 8
+                const int q = static_cast<int>((words[j] >> (4 * nib)) & 15u);
+                const float w = __bfloat162float(__float2bfloat16_rn(static_cast<float>(q - zp[hi]) * sc[hi]));
+                acc[hi] = fmaf(__bfloat162float(a_row[64 * u + dk]), w, acc[hi]);
+            }
     }
-    C[static_cast<size_t>(m) * N + n] = __float2bfloat16_rn(acc);
+    part[threadIdx.x][0] = acc[0], part[threadIdx.x][1] = acc[1];
+    __syncthreads();
+    if (threadIdx.x < 16) {  // column threadIdx.x of the strip: the 4 warps x 4 lanes (g, c = 0..3) that hold it, in order
+        const int gg = threadIdx.x & 7, hi = threadIdx.x >> 3;
+        float sum = 0.f;
+        for (int w = 0; w < 4; ++w)
+            for (int c = 0; c < 4; ++c) sum += part[w * 32 + 4 * gg + c][hi];
+        C[static_cast<size_t>(m) * N + 16 * t + threadIdx.x] = __float2bfloat16_rn(sum);
+    }
 }
 
 // ---- shared by variants 1-3 -----------------------------------------------------------------------
@@ -113,35 +134,66 @@ __device__ __forceinline__ void store_tile(__nv_bfloat16* __restrict__ C, const 
 }
 
 // ---- variant 1 ----------------------------------------------------------------------------------
+// The first tensor-core rung: a CTA per (strip, 32 tokens). The strip's codes are brought into shared memory by the TMA
+// engine, four groups (4 KiB) per bulk copy, double buffered, and are shared by the CTA's four warps, each of which
+// takes its own 8-token tile (one legacy MMA per 16 x 16 weights); scales and zero points come straight from global
+// memory. One bounded barrier wait and one block barrier per 4 KiB.
+constexpr int kStripChunkGroups = 4;
 
 template <bool ASYM>
 __global__ void __launch_bounds__(128)
-w4_strip_kernel(const __nv_bfloat16* __restrict__ A, const uint4* __restrict__ packed,
+w4_strip_kernel(const __nv_bfloat16* __restrict__ A, const unsigned char* __restrict__ packed,
                 const __nv_bfloat16* __restrict__ scales, const uint8_t* __restrict__ zeros,
-                __nv_bfloat16* __restrict__ C, int M, int N, int K) {
-    const int lane = threadIdx.x & 31, gl = lane >> 2, c = lane & 3;
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int tok0 = blockIdx.y * 8;
-    if (t >= N / 16) return;
-    const int G = K / w4::kGroup;
-    const uint4* wp = packed + static_cast<size_t>(t) * G * 64 + lane;
+                __nv_bfloat16* __restrict__ C, int M, int N, int K, int* status) {
+    __shared__ __align__(128) unsigned char codes[2][kStripChunkGroups * w4::kGroupBytes];
+    __shared__ uint64_t landed[2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gl = lane >> 2, c = lane & 3;
+    const int t = blockIdx.x, G = K / w4::kGroup;
+    const int tok0 = blockIdx.y * 32 + warp * 8;          // this warp's token tile
+    const bool has_tokens = tok0 < M;                      // a warp without tokens still keeps the barriers' count
+    const int chunks = (G + kStripChunkGroups - 1) / kStripChunkGroups;
+    const unsigned char* strip = packed + static_cast<size_t>(t) * G * w4::kGroupBytes;
+    auto fetch = [&](int chunk) {  // thread 0 only
+        const int g0 = chunk * kStripChunkGroups, n = min(kStripChunkGroups, G - g0);
+        mbar_arrive_expect_tx(&landed[chunk & 1], static_cast<unsigned>(n * w4::kGroupBytes));
+        bulk_g2s(codes[chunk & 1], strip + static_cast<size_t>(g0) * w4::kGroupBytes, static_cast<unsigned>(n * w4::kGroupBytes),
+                 &landed[chunk & 1]);
+    };
+    if (threadIdx.x == 0) {
+        mbar_init(&landed[0], 1);
+        mbar_init(&landed[1], 1);
+        ptx::fence_mbar_init();
+        fetch(0);
+    }
+    __syncthreads();
     const unsigned short* sp = reinterpret_cast<const unsigned short*>(scales) + 16 * t + gl;
     const uint8_t* zp = zeros + 16 * t + gl;
     float acc[1][1][4] = {{{0.f, 0.f, 0.f, 0.f}}};
-    for (int g = 0; g < G; ++g) {
-        ActGroup act[1] = {load_acts(A, tok0 + gl, M, K, g, c)};
-        const uint4 q0 = ptx::ldg_stream(wp + (2 * g) * 32), q1 = ptx::ldg_stream(wp + (2 * g + 1) * 32);
-        const uint32_t s_lo = w4::splat16(sp[static_cast<size_t>(g) * N]);
-        const uint32_t s_hi = w4::splat16(sp[static_cast<size_t>(g) * N + 8]);
-        uint32_t o_lo = w4::kSymOffset, o_hi = w4::kSymOffset;
-        if (ASYM) {
-            o_lo = w4::offset_pair(zp[static_cast<size_t>(g) * N]);
-            o_hi = w4::offset_pair(zp[static_cast<size_t>(g) * N + 8]);
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        if (threadIdx.x == 0 && chunk + 1 < chunks) fetch(chunk + 1);  // its buffer was released by the barrier below
+        // bounded; the block leaves together or not at all
+        if (!__syncthreads_and(mbar_wait(&landed[chunk & 1], (chunk >> 1) & 1, status))) return;
+        const int g0 = chunk * kStripChunkGroups, n = min(kStripChunkGroups, G - g0);
+        if (has_tokens) {
+            const uint4* cw = reinterpret_cast<const uint4*>(codes[chunk & 1]) + lane;
+            for (int gi = 0; gi < n; ++gi) {
+                const int g = g0 + gi;
+                ActGroup act[1] = {load_acts(A, tok0 + gl, M, K, g, c)};
+                const uint4 q0 = cw[(2 * gi) * 32], q1 = cw[(2 * gi + 1) * 32];
+                const uint32_t s_lo = w4::splat16(sp[static_cast<size_t>(g) * N]);
+                const uint32_t s_hi = w4::splat16(sp[static_cast<size_t>(g) * N + 8]);
+                uint32_t o_lo = w4::kSymOffset, o_hi = w4::kSymOffset;
+                if (ASYM) {
+                    o_lo = w4::offset_pair(zp[static_cast<size_t>(g) * N]);
+                    o_hi = w4::offset_pair(zp[static_cast<size_t>(g) * N + 8]);
+                }
+                unit_mma<1, 1>(acc, q0, 0, o_lo, o_hi, s_lo, s_hi, act);
+                unit_mma<1, 1>(acc, q1, 1, o_lo, o_hi, s_lo, s_hi, act);
+            }
         }
-        unit_mma<1, 1>(acc, q0, 0, o_lo, o_hi, s_lo, s_hi, act);
-        unit_mma<1, 1>(acc, q1, 1, o_lo, o_hi, s_lo, s_hi, act);
+        __syncthreads();  // every warp is done with this buffer before the copy after next overwrites it
     }
-    store_tile(C, acc[0][0], tok0, M, N, 16 * t, lane);
+    if (has_tokens) store_tile(C, acc[0][0], tok0, M, N, 16 * t, lane);
 }
 
 // ---- variants 2 and 3: the weight stream ------------------------------------------------------------
@@ -755,17 +807,22 @@ extern "C" int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void*
     const auto* sc = static_cast<const __nv_bfloat16*>(scales);
     auto* c = static_cast<__nv_bfloat16*>(C);
     if (variant == 0) {
-        const dim3 grid(cdiv(N, 128), M);
-        w4_naive_kernel<<<grid, 128, 0, stream>>>(a, reinterpret_cast<const uint32_t*>(packed), sc, zeros, c, M, N, K);
+        SPK_REQUIRE(M <= 65535, "w4gemm: variant 0 takes at most 65535 tokens, got %d", M);
+        const dim3 grid(N / 16, M);
+        w4_scalar_kernel<<<grid, 128, 0, stream>>>(a, reinterpret_cast<const uint4*>(packed), sc, zeros, c, M, N, K);
         SPK_CHECK_LAUNCH();
         return SPK_OK;
     }
     if (variant == 1) {
-        const dim3 grid(cdiv(N / 16, 4), cdiv(M, 8));
+        DeviceState* dev = nullptr;
+        if (int rc = device_state(&dev)) return rc;
+        const dim3 grid(N / 16, cdiv(M, 32));
+        SPK_REQUIRE(grid.y <= 65535, "w4gemm: variant 1 takes at most 2097120 tokens, got %d", M);
+        const auto* codes = reinterpret_cast<const unsigned char*>(packed);
         if (zeros)
-            w4_strip_kernel<true><<<grid, 128, 0, stream>>>(a, reinterpret_cast<const uint4*>(packed), sc, zeros, c, M, N, K);
+            w4_strip_kernel<true><<<grid, 128, 0, stream>>>(a, codes, sc, zeros, c, M, N, K, dev->status);
         else
-            w4_strip_kernel<false><<<grid, 128, 0, stream>>>(a, reinterpret_cast<const uint4*>(packed), sc, zeros, c, M, N, K);
+            w4_strip_kernel<false><<<grid, 128, 0, stream>>>(a, codes, sc, zeros, c, M, N, K, dev->status);
         SPK_CHECK_LAUNCH();
         return SPK_OK;
     }
