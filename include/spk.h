@@ -64,7 +64,7 @@ SPK_API int spk_w4_quantize_bf16(const void* W, int32_t* qweight, void* scales, 
 SPK_API int spk_w4_repack(const int32_t* qweight, int32_t* packed, int K, int N, void* stream);
 /* reference include/spark/kernels.h:411-413 (w4gemm_bf16): C bf16 [M][N] = A bf16 [M][K] times
  * bf16((q - z) * s). N % 16 == 0, K % 128 == 0, M >= 1, 16-byte aligned A, packed, scales,
- * zeros. variant 0 naive, 1 warp per strip, 2 tuned (default), 3 batch invariant. */
+ * zeros. variant 0 scalar (walks the packed layout), 1 CTA per strip with TMA-staged codes and warp MMA, 2 tuned (default), 3 batch invariant. */
 SPK_API int spk_w4gemm_bf16(const void* A, const int32_t* packed, const void* scales,
                             const uint8_t* zeros, void* C, int M, int N, int K, int variant,
                             void* stream);
